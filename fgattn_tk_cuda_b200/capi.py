@@ -1,0 +1,179 @@
+"""ctypes binding of the C ABI declared in include/fgattn_b200.h.
+
+This is the only route from Python to the kernels; there is no fallback.  Importing works without a
+GPU (so the symbol table can be checked), calling needs one.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "libfgattn_b200.so"
+
+OK = 0
+STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "UNSUPPORTED", 3: "MISALIGNED", 4: "CUDA_ERROR", 5: "NO_DRIVER",
+                6: "DEVICE_TIMEOUT", 7: "SCRATCH_TOO_SMALL"}
+
+_vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/fgattn_b200.h one to one
+PROTOTYPES = {
+    "fgattn_status_string": (C.c_char_p, [_i]),
+    "fgattn_last_cuda_error": (_i, []),
+    "fgattn_check": (_i, [_vp, C.POINTER(_i)]),
+    "fgattn_full_attn": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_fullattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_booleanmask_128": (_i, [_vp, _f, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_booleanmask_to_indexmask": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "fgattn_all_index_mask": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "fgattn_sp_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_block_scratch_bytes": (_sz, [_i, _i, _i, _i]),
+    "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f, _vp,
+                                      _sz, _vp]),
+    "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+}
+
+_lib = None
+
+
+class FgattnError(RuntimeError):
+    def __init__(self, fn: str, status: int, detail: str = ""):
+        self.status = status
+        super().__init__(f"{fn} failed: {STATUS_NAMES.get(status, status)} {detail}".strip())
+
+
+def lib() -> C.CDLL:
+    """Load libfgattn_b200.so (built in-tree by fgattn_tk_cuda_b200._build).  Raises if absent."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(f"{_LIB_PATH} is missing: build it with `python -m fgattn_tk_cuda_b200._build` "
+                              "(there is no CPU or PyTorch fallback)")
+        l = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _call(name: str, *args):
+    st = getattr(lib(), name)(*args)
+    if st != OK:
+        detail = lib().fgattn_status_string(st).decode()
+        if st == 4:
+            detail += f" (cudaError {lib().fgattn_last_cuda_error()})"
+        raise FgattnError(name, st, detail)
+
+
+def _check_qkv(*ts):
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise FgattnError("argument check", 1, "tensors must live on a CUDA device")
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.dim() != 4:
+            raise FgattnError("argument check", 1, "q/k/v/o must be contiguous bf16 [B,H,S,D]")
+
+
+def check(device=None) -> None:
+    """Synchronise the current stream and raise if a kernel gave up on a bounded wait."""
+    code = _i(0)
+    with torch.cuda.device(device):
+        st = lib().fgattn_check(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(code))
+    if st != OK:
+        raise FgattnError("fgattn_check", st, f"wait id {code.value}")
+
+
+def full_attn(o, q, k, v, kv_seq_len=None, scale=0.0):
+    _check_qkv(o, q, k, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_full_attn", _ptr(o), _ptr(q), _ptr(k), _ptr(v), B, H, S, D, kv_seq_len or S, scale, _stream(q))
+
+
+def fullattn_maxq_denom(o, max_q, denom, q, k, v, kv_seq_len=None, scale=0.0):
+    _check_qkv(o, q, k, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_fullattn_maxq_denom", _ptr(o), _ptr(max_q), _ptr(denom), _ptr(q), _ptr(k), _ptr(v), B, H, S, D,
+              kv_seq_len or S, scale, _stream(q))
+
+
+def maxq_denom(max_q, denom, q, k, kv_seq_len=None, scale=0.0):
+    _check_qkv(q, k)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_maxq_denom", _ptr(max_q), _ptr(denom), _ptr(q), _ptr(k), B, H, S, D, kv_seq_len or S, scale,
+              _stream(q))
+
+
+def booleanmask_128(booleanmask, max_q, denom, q, k, threshold, kv_seq_len=None, scale=0.0):
+    _check_qkv(q, k)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_booleanmask_128", _ptr(booleanmask), float(threshold), booleanmask.shape[3], _ptr(max_q),
+              _ptr(denom), _ptr(q), _ptr(k), B, H, S, D, kv_seq_len or S, scale, _stream(q))
+
+
+def booleanmask_to_indexmask(kv_indices, kv_num_indices, booleanmask, seq):
+    B, H, SB, stride = booleanmask.shape
+    with torch.cuda.device(booleanmask.device):
+        _call("fgattn_booleanmask_to_indexmask", _ptr(kv_indices), _ptr(kv_num_indices), _ptr(booleanmask), B, H,
+              int(seq), SB, stride, _stream(booleanmask))
+
+
+def all_index_mask(kv_indices, kv_num_indices, batch, heads, seqblocks, seq):
+    with torch.cuda.device(kv_indices.device):
+        _call("fgattn_all_index_mask", _ptr(kv_indices), _ptr(kv_num_indices), batch, heads, seqblocks, seq,
+              kv_indices.shape[3], _stream(kv_indices))
+
+
+def sp_attn(o, q, k, v, kv_indices, kv_num_indices, scale=0.0):
+    _check_qkv(o, q, k, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_sp_attn", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kv_indices), _ptr(kv_num_indices),
+              kv_indices.shape[3], B, H, S, D, scale, _stream(q))
+
+
+def block_scratch_bytes(B, H, S, kv_seq_len=None) -> int:
+    return int(lib().fgattn_block_scratch_bytes(B, H, S, kv_seq_len or S))
+
+
+def block_index_lists(kb_indices, kb_counts, max_q, denom, q, k, threshold, scratch, o=None, v=None, kv_seq_len=None,
+                      scale=0.0):
+    _check_qkv(q, k, o, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_block_index_lists", _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3], _ptr(max_q),
+              _ptr(denom), _ptr(o), _ptr(q), _ptr(k), _ptr(v), float(threshold), B, H, S, D, kv_seq_len or S, scale,
+              _ptr(scratch), scratch.numel() * scratch.element_size(), _stream(q))
+
+
+def sp_attn_blocks_ml(o, q, k, v, kb_indices, kb_counts, max_q, denom, kv_seq_len=None, scale=0.0):
+    _check_qkv(o, q, k, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_sp_attn_blocks_ml", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
+              kb_indices.shape[3], _ptr(max_q), _ptr(denom), B, H, S, D, kv_seq_len or S, scale, _stream(q))
+
+
+def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0):
+    _check_qkv(o, q, k, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_sp_attn_blocks", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
+              kb_indices.shape[3], B, H, S, D, kv_seq_len or S, scale, _stream(q))

@@ -1,0 +1,321 @@
+// Dense attention family for sm_100a (tcgen05 / TMEM / TMA), one kernel template:
+//   kFull      : O = softmax(Q K^T * scale) V                       (full_attn)
+//   kFullML    : O plus per-row raw max m and denominator l         (fullattn_maxq_denom)
+//   kML        : m and l only, no V                                 (maxq_denom)
+// each optionally emitting, per query row and per 64-key block, the raw block maximum of Q K^T
+// (the input of the threshold epilogue that builds key-block lists), and
+//   kTokenMask : with m, l given, the 128-row x 1-token threshold mask (booleanmask_128).
+//
+// One CTA owns two 128-row query tiles that share every K/V tile.  Warp roles:
+//   warps 0-3  softmax of query tile 0 (one row per thread)      warp 8  TMA producer
+//   warps 4-7  softmax of query tile 1                            warp 9  UMMA issuer
+// S = Q K^T accumulates in tensor memory; the softmax warps read it with tcgen05.ld, write the
+// bf16 probabilities back over the same columns and the PV product takes them from tensor memory.
+#pragma once
+#include "sm100_ptx.cuh"
+#include "softmax_steps.cuh"
+
+namespace fg {
+
+enum DenseMode : int { kFull = 0, kFullML = 1, kML = 2, kTokenMask = 3 };
+
+struct DenseParams {
+  // outputs
+  __nv_bfloat16* o;     // [BH, S, D]
+  float* max_q;         // [BH, S_pad128]   (kTokenMask: input)
+  float* denom;         // [BH, S_pad128]   (kTokenMask: input)
+  float* blockmax;      // [BH(chunk), nkb, S_pad128] raw per-row maxima of each 64-key block, or null
+  int* tokenmask;       // [BH, nqb128, mask_stride]  (kTokenMask)
+  int* err;             // device error word
+  int S, S_pad, kv_len, n_kv_tiles, nkb, mask_stride;
+  int bh0;              // first (batch*head) unit of this launch (blockmax is relative to it)
+  float scale_log2;     // softmax scale * log2(e)
+  float log2_tau;       // kTokenMask
+};
+
+template <int D>
+struct DenseCfg {
+  static constexpr int kHalves = D / 64;                 // 128-byte column groups per row
+  static constexpr int kTileBytes = 128 * D * 2;         // one 128-row tile of Q, K or V
+  static constexpr int kKStages = 2, kVStages = 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = 2 * kTileBytes;
+  static constexpr int kOffV = kOffK + kKStages * kTileBytes;
+  static constexpr int kOffBar = kOffV + kVStages * kTileBytes;
+  static constexpr int kSmemBytes = kOffBar + 1024 /*barriers + scratch*/ + 1024 /*alignment slack*/;
+};
+
+// barrier slots (8 bytes each) inside the barrier block
+enum : int {
+  BAR_Q_FULL = 0,
+  BAR_K_FULL = 1,    // +stage (<=4)
+  BAR_K_EMPTY = 5,   // +stage
+  BAR_V_FULL = 9,    // +stage
+  BAR_V_EMPTY = 13,  // +stage
+  BAR_S_FULL = 17,   // +tile*2+buf
+  BAR_S_EMPTY = 21,  // +tile*2+buf
+  BAR_P_FULL = 25,   // +tile
+  BAR_O_FULL = 27,   // +tile
+  BAR_COUNT = 29
+};
+
+template <int D, int MODE, bool BLOCKMAX>
+__global__ void __launch_bounds__(384, 1)
+dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mv, const DenseParams p) {
+  using Cfg = DenseCfg<D>;
+  constexpr bool HAS_V = (MODE == kFull || MODE == kFullML);
+  constexpr bool WRITE_ML = (MODE == kFullML || MODE == kML);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bars = sbase + Cfg::kOffBar;
+  auto bar = [&](int i) -> uint32_t { return bars + 8u * uint32_t(i); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffBar + 8 * BAR_COUNT);
+  AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * BAR_COUNT + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;                  // (batch*head) unit within this launch
+  const int q0 = blockIdx.x * 256;            // first query row of this CTA
+  const int n_tiles = p.n_kv_tiles;
+
+  if (tid == 0) {
+    ab->flag = 0;
+    mbar_init(bar(BAR_Q_FULL), 1);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(bar(BAR_K_FULL + s), 1);
+      mbar_init(bar(BAR_K_EMPTY + s), 1);
+      mbar_init(bar(BAR_V_FULL + s), 1);
+      mbar_init(bar(BAR_V_EMPTY + s), 1);
+      mbar_init(bar(BAR_S_FULL + s), 1);
+      mbar_init(bar(BAR_S_EMPTY + s), 128);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(BAR_P_FULL + t), 128);
+      mbar_init(bar(BAR_O_FULL + t), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    reg_dealloc<72>();
+    if (lane == 0) {
+      tma_prefetch_desc(&mq);
+      tma_prefetch_desc(&mk);
+      if (HAS_V) tma_prefetch_desc(&mv);
+      mbar_arrive_expect_tx(bar(BAR_Q_FULL), 2 * Cfg::kTileBytes);
+      for (int t = 0; t < 2; ++t)
+        for (int h = 0; h < Cfg::kHalves; ++h)
+          tma_load_3d(sbase + Cfg::kOffQ + t * Cfg::kTileBytes + h * 16384, &mq, bar(BAR_Q_FULL), h * 64,
+                      q0 + t * 128, p.bh0 + bh);
+      bool ok = true;
+      int j = 0;
+      for (; j < n_tiles && ok; ++j) {
+        const int ks = j % Cfg::kKStages, kf = j / Cfg::kKStages;
+        if (kf > 0) ok = mbar_wait(bar(BAR_K_EMPTY + ks), (kf - 1) & 1, ab, p.err, 101);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar(BAR_K_FULL + ks), Cfg::kTileBytes);
+        for (int h = 0; h < Cfg::kHalves; ++h)
+          tma_load_3d(sbase + Cfg::kOffK + ks * Cfg::kTileBytes + h * 16384, &mk, bar(BAR_K_FULL + ks), h * 64,
+                      j * 128, p.bh0 + bh);
+        if (HAS_V) {
+          const int vs = j % Cfg::kVStages, vf = j / Cfg::kVStages;
+          if (vf > 0) ok = mbar_wait(bar(BAR_V_EMPTY + vs), (vf - 1) & 1, ab, p.err, 102);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar(BAR_V_FULL + vs), Cfg::kTileBytes);
+          for (int h = 0; h < Cfg::kHalves; ++h)
+            tma_load_3d(sbase + Cfg::kOffV + vs * Cfg::kTileBytes + h * 16384, &mv, bar(BAR_V_FULL + vs), h * 64,
+                        j * 128, p.bh0 + bh);
+        }
+      }
+      if (!ok) {
+        // let copies that are still in flight land before the CTA goes away
+        mbar_wait_brief(bar(BAR_Q_FULL), 0);
+        for (int s = 0; s < Cfg::kKStages; ++s) {
+          int last = -1;
+          for (int jj = s; jj < j + 1 && jj < n_tiles; jj += Cfg::kKStages) last = jj;
+          if (last >= 0) mbar_wait_brief(bar(BAR_K_FULL + s), (last / Cfg::kKStages) & 1);
+          if (HAS_V && last >= 0) mbar_wait_brief(bar(BAR_V_FULL + s), (last / Cfg::kVStages) & 1);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ UMMA issuer
+    reg_dealloc<72>();
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
+      const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
+      auto issue_qk = [&](int t, int kstage, uint32_t d_col) {
+        const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffK + kstage * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_ss(tmem + d_col, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                  idesc_qk, ks > 0);
+        }
+      };
+      auto issue_pv = [&](int t, int vstage, bool acc) {
+        const uint32_t va = sbase + Cfg::kOffV + vstage * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)   // 128 keys, 16 per UMMA
+          umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+                  idesc_pv, (acc || ks > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(bar(BAR_Q_FULL), 0, ab, p.err, 201);
+      if (HAS_V) {
+        if (ok) ok = mbar_wait(bar(BAR_K_FULL + 0), 0, ab, p.err, 202);
+        if (ok) {
+          tc_fence_after();
+          for (int t = 0; t < 2; ++t) {
+            issue_qk(t, 0, t * 128);
+            umma_commit(bar(BAR_S_FULL + t * 2));
+          }
+          umma_commit(bar(BAR_K_EMPTY + 0));
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int vs = j % Cfg::kVStages;
+          ok = mbar_wait(bar(BAR_V_FULL + vs), (j / Cfg::kVStages) & 1, ab, p.err, 203);
+          const bool more = (j + 1 < n_tiles);
+          const int ks = (j + 1) % Cfg::kKStages;
+          if (ok && more) ok = mbar_wait(bar(BAR_K_FULL + ks), ((j + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
+          for (int t = 0; t < 2 && ok; ++t) {
+            ok = mbar_wait(bar(BAR_P_FULL + t), j & 1, ab, p.err, 205);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, vs, j > 0);
+            if (more) {
+              issue_qk(t, ks, t * 128);
+              umma_commit(bar(BAR_S_FULL + t * 2));
+            } else {
+              umma_commit(bar(BAR_O_FULL + t));
+            }
+          }
+          if (ok) {
+            umma_commit(bar(BAR_V_EMPTY + vs));
+            if (more) umma_commit(bar(BAR_K_EMPTY + ks));
+          }
+        }
+      } else {
+        // no V: S is double-buffered per query tile; tile t, buffer b lives at column (2t+b)*128
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const int ks = j % Cfg::kKStages, b = j & 1, f = j >> 1;
+          ok = mbar_wait(bar(BAR_K_FULL + ks), (j / Cfg::kKStages) & 1, ab, p.err, 206);
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (f > 0) ok = mbar_wait(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t, ks, (t * 2 + b) * 128);
+            umma_commit(bar(BAR_S_FULL + t * 2 + b));
+          }
+          if (ok) umma_commit(bar(BAR_K_EMPTY + ks));
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ softmax warpgroups
+    reg_alloc<216>();
+    const int t = warp >> 2;                           // query tile of this warpgroup
+    const int wq = warp & 3;                           // TMEM lane quarter
+    const int row_in_tile = wq * 32 + lane;
+    const int row = q0 + t * 128 + row_in_tile;        // query row in the sequence
+    const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
+    const float c = p.scale_log2;
+    const size_t ml_off = size_t(p.bh0 + bh) * p.S_pad + row;
+
+    OnlineState st;
+    online_init(st);
+    float t_row = INFINITY;       // kTokenMask: m*c + log2(l)
+    if (MODE == kTokenMask) {
+      if (row < p.S) t_row = p.max_q[ml_off] * c + log2f(p.denom[ml_off]);
+    }
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = HAS_V ? 0 : (j & 1);
+      const int fpar = HAS_V ? (j & 1) : ((j >> 1) & 1);
+      ok = mbar_wait(bar(BAR_S_FULL + t * 2 + b), fpar, ab, p.err, 301);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = lane_base + (HAS_V ? t * 128 : (t * 2 + b) * 128);
+      const int kv_left = p.kv_len - j * 128;          // valid keys in this tile
+      const int valid0 = min(64, kv_left), valid1 = max(0, min(64, kv_left - 64));
+      if (MODE == kTokenMask) {
+        // per-token keep bit: any row of the 128-row block with s*c - t_row > log2(tau)
+        const float thr = p.log2_tau + t_row;
+        uint32_t bits[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + w * 32, r);
+          tmem_ld_wait();
+          uint32_t m = 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            m |= (__uint_as_float(r[i]) * c > thr && w * 32 + i < kv_left) ? (1u << i) : 0u;
+          bits[w] = __reduce_or_sync(0xffffffffu, m);
+        }
+        tc_fence_before();
+        mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
+        // the caller-zeroed mask is only ever set: four warps (32 rows each) OR into it
+        if (q0 + t * 128 < p.S) {
+          const int qblk = (q0 + t * 128) >> 7;
+          int* mrow = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + qblk) * p.mask_stride + j * 128;
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            if ((bits[w] >> lane) & 1u) atomicOr(mrow + w * 32 + lane, 1);
+        }
+        continue;
+      }
+      float mx0, mx1;
+      softmax_online_step<D, HAS_V>(s_addr, lane_base + t * 128, lane_base + 256 + t * 128, valid0, valid1, c, j == 0,
+                                    st, mx0, mx1);
+      tc_fence_before();
+      if (HAS_V) mbar_arrive(bar(BAR_P_FULL + t));
+      else mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
+      if (BLOCKMAX) {
+        if (row < p.S_pad) {
+          float* bm = p.blockmax + (size_t(bh) * p.nkb + size_t(j) * 2) * p.S_pad + row;
+          bm[0] = mx0;
+          if (j * 2 + 1 < p.nkb) bm[p.S_pad] = mx1;
+        }
+      }
+    }
+    // ---- epilogue
+    if (ok && WRITE_ML) {
+      if (row < p.S) {
+        p.max_q[ml_off] = st.m_true;
+        p.denom[ml_off] = st.l * ex2(st.m_used - st.m_true * c);
+      } else if (row < p.S_pad) {
+        p.max_q[ml_off] = 0.f;
+        p.denom[ml_off] = -INFINITY;
+      }
+    }
+    if (ok && HAS_V) {
+      ok = mbar_wait(bar(BAR_O_FULL + t), 0, ab, p.err, 302);
+      if (ok) {
+        tc_fence_after();
+        store_o_row<D>(lane_base + 256 + t * 128, p.o + (size_t(p.bh0 + bh) * p.S + row) * D, 1.0f / st.l, row < p.S);
+      }
+    }
+  }
+  else {
+    reg_dealloc<72>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace fg

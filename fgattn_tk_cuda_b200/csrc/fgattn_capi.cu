@@ -1,0 +1,341 @@
+// extern "C" entry points of libfgattn_b200: argument checks, TMA tensor maps, launches.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <algorithm>
+#include <mutex>
+
+#include "../../include/fgattn_b200.h"
+#include "dense_attn.cuh"
+#include "mask_kernels.cuh"
+#include "sparse_attn.cuh"
+#include "tensor_map.h"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+std::mutex g_mutex;
+int* g_err_word[64] = {nullptr};
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = int(e);
+  return FGATTN_CUDA_ERROR;
+}
+#define FG_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e__ = (call);                           \
+    if (e__ != cudaSuccess) return cuda_fail(e__);      \
+  } while (0)
+
+// 4-byte per-device error word that bounded in-kernel waits write to.
+int get_err_word(int** out) {
+  int dev = 0;
+  FG_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FGATTN_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_err_word[dev]) {
+    int* p = nullptr;
+    FG_CUDA(cudaMalloc(&p, sizeof(int)));
+    FG_CUDA(cudaMemset(p, 0, sizeof(int)));
+    g_err_word[dev] = p;
+  }
+  *out = g_err_word[dev];
+  return FGATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_qk(const void* q, const void* k, int B, int H, int S, int D, int kv_len) {
+  if (!q || !k) return FGATTN_INVALID_ARGUMENT;
+  if (B <= 0 || H <= 0 || S <= 0) return FGATTN_INVALID_ARGUMENT;
+  if (D != 64 && D != 128) return FGATTN_UNSUPPORTED;
+  if (kv_len < 1 || kv_len > S) return FGATTN_INVALID_ARGUMENT;
+  if ((long long)B * H > 65535) return FGATTN_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k)) return FGATTN_MISALIGNED;
+  return FGATTN_OK;
+}
+
+float resolve_scale_log2(float scale, int D) {
+  const float s = (scale > 0.f) ? scale : 1.0f / sqrtf(float(D));
+  return s * 1.4426950408889634f;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return FGATTN_OK;
+}
+
+// One launch of the dense family over heads [bh0, bh0 + nbh).
+template <int D, int MODE, bool BLOCKMAX>
+int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const fg::DenseParams& p,
+                   int nbh, cudaStream_t st) {
+  auto kern = fg::dense_attn_kernel<D, MODE, BLOCKMAX>;
+  int r = set_smem(kern, fg::DenseCfg<D>::kSmemBytes);
+  if (r) return r;
+  dim3 grid((p.S + 255) / 256, nbh, 1);
+  kern<<<grid, 384, fg::DenseCfg<D>::kSmemBytes, st>>>(mq, mk, mv, p);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+template <int MODE, bool BLOCKMAX>
+int launch_dense(int D, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const fg::DenseParams& p,
+                 int nbh, cudaStream_t st) {
+  return D == 128 ? launch_dense_t<128, MODE, BLOCKMAX>(mq, mk, mv, p, nbh, st)
+                  : launch_dense_t<64, MODE, BLOCKMAX>(mq, mk, mv, p, nbh, st);
+}
+
+struct DenseSetup {
+  CUtensorMap mq, mk, mv;
+  fg::DenseParams p;
+};
+
+int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int B, int H, int S, int D, int kv_len,
+                float scale) {
+  int r = check_qk(q, k, B, H, S, D, kv_len);
+  if (r) return r;
+  if (v && !aligned16(v)) return FGATTN_MISALIGNED;
+  if (fg::make_qkv_map(&s.mq, q, B * H, S, D, 128) || fg::make_qkv_map(&s.mk, k, B * H, S, D, 128) ||
+      fg::make_qkv_map(&s.mv, v ? v : k, B * H, S, D, 128))
+    return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
+  memset(&s.p, 0, sizeof(s.p));
+  s.p.S = S;
+  s.p.S_pad = ((S + 127) / 128) * 128;
+  s.p.kv_len = kv_len;
+  s.p.n_kv_tiles = (kv_len + 127) / 128;
+  s.p.nkb = (kv_len + 63) / 64;
+  s.p.scale_log2 = resolve_scale_log2(scale, D);
+  return get_err_word(&s.p.err);
+}
+
+template <bool RENORM>
+int launch_sparse(void* o, const void* q, const void* k, const void* v, const int* kb_idx, const int* kb_cnt,
+                  int list_stride, const float* max_q, const float* denom, int B, int H, int S, int D, int kv_len,
+                  float scale, cudaStream_t st) {
+  int r = check_qk(q, k, B, H, S, D, kv_len);
+  if (r) return r;
+  if (!o || !v || !kb_idx || !kb_cnt) return FGATTN_INVALID_ARGUMENT;
+  if (!RENORM && (!max_q || !denom)) return FGATTN_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(v)) return FGATTN_MISALIGNED;
+  fg::SparseParams p;
+  memset(&p, 0, sizeof(p));
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.max_q = max_q;
+  p.denom = denom;
+  p.kb_idx = kb_idx;
+  p.kb_cnt = kb_cnt;
+  p.S = S;
+  p.S_pad = ((S + 127) / 128) * 128;
+  p.kv_len = kv_len;
+  p.nqb = (S + 63) / 64;
+  p.nkb = (kv_len + 63) / 64;
+  p.list_stride = list_stride;
+  p.list_cap = p.nkb + 2;
+  p.scale_log2 = resolve_scale_log2(scale, D);
+  if (list_stride < 1) return FGATTN_INVALID_ARGUMENT;
+  r = get_err_word(&p.err);
+  if (r) return r;
+  CUtensorMap mq, mk, mv;
+  if (fg::make_qkv_map(&mq, q, B * H, S, D, 128) || fg::make_qkv_map(&mk, k, B * H, S, D, 64) ||
+      fg::make_qkv_map(&mv, v, B * H, S, D, 64))
+    return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
+  dim3 grid((S + 255) / 256, B * H, 1);
+  if (D == 128) {
+    const int smem = fg::SparseCfg<128>::smem_bytes(p.list_cap, p.nkb);
+    if (smem > 232448) return FGATTN_UNSUPPORTED;
+    auto kern = fg::sparse_block_attn_kernel<128, RENORM>;
+    r = set_smem(kern, smem);
+    if (r) return r;
+    kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
+  } else {
+    const int smem = fg::SparseCfg<64>::smem_bytes(p.list_cap, p.nkb);
+    if (smem > 232448) return FGATTN_UNSUPPORTED;
+    auto kern = fg::sparse_block_attn_kernel<64, RENORM>;
+    r = set_smem(kern, smem);
+    if (r) return r;
+    kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
+  }
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* fgattn_status_string(int status) {
+  switch (status) {
+    case FGATTN_OK: return "ok";
+    case FGATTN_INVALID_ARGUMENT: return "invalid argument";
+    case FGATTN_UNSUPPORTED: return "unsupported shape or size";
+    case FGATTN_MISALIGNED: return "tensor base address is not 16-byte aligned";
+    case FGATTN_CUDA_ERROR: return "CUDA error";
+    case FGATTN_NO_DRIVER: return "CUDA driver tensor-map encoder not available";
+    case FGATTN_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case FGATTN_SCRATCH_TOO_SMALL: return "scratch buffer too small";
+    default: return "unknown status";
+  }
+}
+
+int fgattn_last_cuda_error(void) { return g_last_cuda_error; }
+
+int fgattn_check(void* stream, int* code) {
+  int* w = nullptr;
+  int r = get_err_word(&w);
+  if (r) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FG_CUDA(cudaStreamSynchronize(st));
+  int h = 0;
+  FG_CUDA(cudaMemcpy(&h, w, sizeof(int), cudaMemcpyDeviceToHost));
+  if (code) *code = h;
+  if (h != 0) {
+    FG_CUDA(cudaMemset(w, 0, sizeof(int)));
+    return FGATTN_DEVICE_TIMEOUT;
+  }
+  return FGATTN_OK;
+}
+
+int fgattn_full_attn(void* o, const void* q, const void* k, const void* v, int batch, int heads, int seq, int D,
+                     int kv_seq_len, float scale, void* stream) {
+  if (!o || !v) return FGATTN_INVALID_ARGUMENT;
+  if (!aligned16(o)) return FGATTN_MISALIGNED;
+  DenseSetup s;
+  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_seq_len, scale);
+  if (r) return r;
+  s.p.o = static_cast<__nv_bfloat16*>(o);
+  return launch_dense<fg::kFull, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, static_cast<cudaStream_t>(stream));
+}
+
+int fgattn_fullattn_maxq_denom(void* o, float* max_q, float* denom, const void* q, const void* k, const void* v,
+                               int batch, int heads, int seq, int D, int kv_seq_len, float scale, void* stream) {
+  if (!o || !v || !max_q || !denom) return FGATTN_INVALID_ARGUMENT;
+  if (!aligned16(o)) return FGATTN_MISALIGNED;
+  DenseSetup s;
+  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_seq_len, scale);
+  if (r) return r;
+  s.p.o = static_cast<__nv_bfloat16*>(o);
+  s.p.max_q = max_q;
+  s.p.denom = denom;
+  return launch_dense<fg::kFullML, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, static_cast<cudaStream_t>(stream));
+}
+
+int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, int batch, int heads, int seq, int D,
+                      int kv_seq_len, float scale, void* stream) {
+  if (!max_q || !denom) return FGATTN_INVALID_ARGUMENT;
+  DenseSetup s;
+  int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_seq_len, scale);
+  if (r) return r;
+  s.p.max_q = max_q;
+  s.p.denom = denom;
+  return launch_dense<fg::kML, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, static_cast<cudaStream_t>(stream));
+}
+
+int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
+                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_seq_len,
+                           float scale, void* stream) {
+  if (!booleanmask || !max_q || !denom || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
+  if (mask_stride < kv_seq_len) return FGATTN_INVALID_ARGUMENT;
+  DenseSetup s;
+  int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_seq_len, scale);
+  if (r) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t n = size_t(batch) * heads * ((seq + 127) / 128) * mask_stride;
+  FG_CUDA(cudaMemsetAsync(booleanmask, 0, n * sizeof(int), st));
+  s.p.max_q = const_cast<float*>(max_q);
+  s.p.denom = const_cast<float*>(denom);
+  s.p.tokenmask = booleanmask;
+  s.p.mask_stride = mask_stride;
+  s.p.log2_tau = log2f(threshold);
+  return launch_dense<fg::kTokenMask, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, st);
+}
+
+int fgattn_booleanmask_to_indexmask(int* kv_indices, int* kv_num_indices, const int* booleanmask, int batch, int heads,
+                                    int seq, int seqblocks, int mask_stride, void* stream) {
+  if (!kv_indices || !kv_num_indices || !booleanmask) return FGATTN_INVALID_ARGUMENT;
+  if (batch <= 0 || heads <= 0 || seqblocks <= 0 || mask_stride <= 0 || seq < 0) return FGATTN_INVALID_ARGUMENT;
+  const long long rows = (long long)batch * heads * seqblocks;
+  if (rows > 2147483647LL) return FGATTN_UNSUPPORTED;
+  fg::mask_to_index_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      booleanmask, kv_indices, kv_num_indices, mask_stride, seq);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int heads, int seqblocks, int seq,
+                          int index_stride, void* stream) {
+  if (!kv_indices || !kv_num_indices) return FGATTN_INVALID_ARGUMENT;
+  if (batch <= 0 || heads <= 0 || seqblocks <= 0 || index_stride <= 0 || seq < 0) return FGATTN_INVALID_ARGUMENT;
+  const long long rows = (long long)batch * heads * seqblocks;
+  if (rows > 2147483647LL) return FGATTN_UNSUPPORTED;
+  fg::identity_index_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(kv_indices, kv_num_indices,
+                                                                                          index_stride, seq);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
+                   const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, float scale,
+                   void* stream) {
+  (void)o; (void)q; (void)k; (void)v; (void)kv_indices; (void)kv_num_indices; (void)mask_stride;
+  (void)batch; (void)heads; (void)seq; (void)D; (void)scale; (void)stream;
+  return FGATTN_UNSUPPORTED;
+}
+
+size_t fgattn_block_scratch_bytes(int batch, int heads, int seq, int kv_seq_len) {
+  if (batch <= 0 || heads <= 0 || seq <= 0 || kv_seq_len <= 0) return 0;
+  const size_t s_pad = size_t((seq + 127) / 128) * 128, nkb = size_t((kv_seq_len + 63) / 64);
+  return size_t(batch) * heads * nkb * s_pad * sizeof(float);
+}
+
+int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, float* max_q, float* denom, void* o,
+                             const void* q, const void* k, const void* v, float threshold, int batch, int heads,
+                             int seq, int D, int kv_seq_len, float scale, void* scratch, size_t scratch_bytes,
+                             void* stream) {
+  if (!kb_indices || !kb_counts || !max_q || !denom || !scratch || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
+  if ((o == nullptr) != (v == nullptr)) return FGATTN_INVALID_ARGUMENT;
+  if (o && !aligned16(o)) return FGATTN_MISALIGNED;
+  DenseSetup s;
+  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_seq_len, scale);
+  if (r) return r;
+  const int nkb = s.p.nkb, nqb = (seq + 63) / 64;
+  if (list_stride < nkb) return FGATTN_INVALID_ARGUMENT;
+  const size_t per_head = size_t(nkb) * s.p.S_pad * sizeof(float);
+  const int chunk = int(std::min<size_t>(scratch_bytes / per_head, size_t(batch) * heads));
+  if (chunk < 1) return FGATTN_SCRATCH_TOO_SMALL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  s.p.o = static_cast<__nv_bfloat16*>(o);
+  s.p.max_q = max_q;
+  s.p.denom = denom;
+  s.p.blockmax = static_cast<float*>(scratch);
+  const float log2_tau = log2f(threshold);
+  const int total = batch * heads;
+  for (int bh0 = 0; bh0 < total; bh0 += chunk) {
+    const int n = std::min(chunk, total - bh0);
+    s.p.bh0 = bh0;
+    r = o ? launch_dense<fg::kFullML, true>(D, s.mq, s.mk, s.mv, s.p, n, st)
+          : launch_dense<fg::kML, true>(D, s.mq, s.mk, s.mv, s.p, n, st);
+    if (r) return r;
+    const int smem = 64 * int(sizeof(float)) + ((nkb + 15) / 16) * 16;
+    fg::block_threshold_compact_kernel<<<dim3(nqb, n), 256, smem, st>>>(
+        s.p.blockmax, max_q, denom, kb_indices, kb_counts, seq, s.p.S_pad, nqb, nkb, list_stride, bh0, s.p.scale_log2,
+        log2_tau);
+    FG_CUDA(cudaGetLastError());
+  }
+  return FGATTN_OK;
+}
+
+int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                             const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
+                             int heads, int seq, int D, int kv_seq_len, float scale, void* stream) {
+  return launch_sparse<false>(o, q, k, v, kb_indices, kb_counts, list_stride, max_q, denom, batch, heads, seq, D,
+                              kv_seq_len, scale, static_cast<cudaStream_t>(stream));
+}
+
+int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                          const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_seq_len,
+                          float scale, void* stream) {
+  return launch_sparse<true>(o, q, k, v, kb_indices, kb_counts, list_stride, nullptr, nullptr, batch, heads, seq, D,
+                             kv_seq_len, scale, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,128 @@
+// Integer / HBM-bound kernels of the mask pipeline: threshold epilogue over block maxima,
+// stream compaction of masks into ascending index lists, identity lists.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fg {
+
+// ---------------------------------------------------------------------------------------------
+// Threshold epilogue + compaction for 64x64 blocks.
+// blockmax[bh][kb][row] holds max_j q_row.k_j (raw) over the keys of block kb.  A block (qb, kb)
+// is kept iff max over the 64 rows of  blockmax*c - (m*c + log2 l)  >  log2(tau), i.e. iff the
+// largest softmax probability inside the block exceeds tau (strict).  Output: ascending key-block
+// list per query block, unused slots = nkb, and the count.
+// grid (nqb, heads_in_chunk), 256 threads; dynamic shared memory: 64 floats + nkb bytes.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+block_threshold_compact_kernel(const float* __restrict__ blockmax, const float* __restrict__ max_q,
+                               const float* __restrict__ denom, int* __restrict__ kb_idx, int* __restrict__ kb_cnt,
+                               int S, int S_pad, int nqb, int nkb, int list_stride, int bh0, float scale_log2,
+                               float log2_tau) {
+  extern __shared__ uint8_t sm[];
+  float* t_row = reinterpret_cast<float*>(sm);
+  uint8_t* keep = sm + 64 * sizeof(float);
+  const int qb = blockIdx.x, bhl = blockIdx.y, bh = bh0 + bhl;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r0 = qb * 64;
+  if (tid < 64) {
+    const int row = r0 + tid;
+    float t = INFINITY;
+    if (row < S) t = max_q[size_t(bh) * S_pad + row] * scale_log2 + log2f(denom[size_t(bh) * S_pad + row]);
+    t_row[tid] = t;
+  }
+  __syncthreads();
+  const float t0 = t_row[lane], t1 = t_row[lane + 32];
+  for (int kb = warp; kb < nkb; kb += 8) {
+    const float* src = blockmax + (size_t(bhl) * nkb + kb) * S_pad + r0;
+    float v = fmaxf(fmaf(src[lane], scale_log2, -t0), fmaf(src[lane + 32], scale_log2, -t1));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) keep[kb] = (v > log2_tau) ? 1 : 0;
+  }
+  __syncthreads();
+  int* out = kb_idx + (size_t(bh) * nqb + qb) * list_stride;
+  if (warp == 0) {
+    int base = 0;
+    for (int kb0 = 0; kb0 < nkb; kb0 += 32) {
+      const int kb = kb0 + lane;
+      const bool k = (kb < nkb) && keep[kb];
+      const uint32_t bal = __ballot_sync(0xffffffffu, k);
+      if (k) out[base + __popc(bal & ((1u << lane) - 1u))] = kb;
+      base += __popc(bal);
+    }
+    if (lane == 0) {
+      kb_cnt[size_t(bh) * nqb + qb] = base;
+      reinterpret_cast<int*>(t_row)[0] = base;
+    }
+  }
+  __syncthreads();
+  const int count = reinterpret_cast<int*>(t_row)[0];
+  for (int i = count + tid; i < list_stride; i += 256) out[i] = nkb;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Mask row -> ascending index list + count (deterministic replacement of an atomic-ticket scan).
+// mask int32 [rows, stride], entry kept iff mask > 0 and column < n_valid.  Unused list slots are
+// written with `stride`.  grid (rows), 256 threads.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+mask_to_index_kernel(const int* __restrict__ mask, int* __restrict__ idx, int* __restrict__ cnt, int stride,
+                     int n_valid) {
+  __shared__ int warp_tot[8];
+  __shared__ int s_base;
+  const size_t rowoff = size_t(blockIdx.x) * stride;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* src = mask + rowoff;
+  int* dst = idx + rowoff;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  const bool vec = ((stride & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (int c0 = 0; c0 < stride; c0 += 1024) {
+    const int col = c0 + tid * 4;
+    int v[4] = {0, 0, 0, 0};
+    if (vec && col + 3 < stride) {
+      const int4 x = *reinterpret_cast<const int4*>(src + col);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (col + e < stride) v[e] = src[col + e];
+    }
+    int f[4], c = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      f[e] = (v[e] > 0 && col + e < n_valid) ? 1 : 0;
+      c += f[e];
+    }
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int off = s_base;
+    for (int w = 0; w < warp; ++w) off += warp_tot[w];
+    off += incl - c;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (f[e]) dst[off++] = col + e;
+    __syncthreads();
+    if (tid == 255) s_base = off;          // last thread's running offset = total so far
+    __syncthreads();
+  }
+  const int total = s_base;
+  if (tid == 0) cnt[blockIdx.x] = total;
+  for (int i = total + tid; i < stride; i += 256) dst[i] = stride;
+}
+
+// Identity lists: idx[row][s] = s for every slot, count = n_keep.
+__global__ void identity_index_kernel(int* __restrict__ idx, int* __restrict__ cnt, int stride, int n_keep) {
+  int* dst = idx + size_t(blockIdx.x) * stride;
+  for (int i = threadIdx.x; i < stride; i += blockDim.x) dst[i] = i;
+  if (threadIdx.x == 0) cnt[blockIdx.x] = n_keep;
+}
+
+}  // namespace fg

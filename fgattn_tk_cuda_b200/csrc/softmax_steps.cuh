@@ -1,0 +1,151 @@
+// Per-thread softmax steps shared by the dense and the block-sparse kernels.  A thread owns one
+// query row (one TMEM lane) and sees one 128-key score tile as two 64-key halves; `valid0` and
+// `valid1` give the number of live columns in each half (0..64), the rest is masked out.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace fg {
+
+struct OnlineState {
+  float m_used;   // running maximum in the scaled log2 domain (s * c); may lag the true one by < 8
+  float m_true;   // exact running raw maximum
+  float l;        // running denominator relative to m_used
+};
+
+__device__ __forceinline__ void online_init(OnlineState& st) {
+  st.m_used = -1.0e30f;
+  st.m_true = -INFINITY;
+  st.l = 0.f;
+}
+
+template <int N>
+__device__ __forceinline__ void mask_cols(uint32_t (&r)[N], int valid) {
+  if (valid < N) {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (i >= valid) r[i] = __float_as_uint(-INFINITY);
+  }
+}
+
+// Online softmax over one score tile.
+//   s_addr : TMEM address (lane already folded in) of the 128 fp32 score columns
+//   p_addr : where the 64 packed-bf16 probability columns go (WRITE_P)
+//   o_addr : the row's D fp32 output accumulator columns (rescaled in place when the maximum grows)
+// Returns the raw maxima of the two 64-key halves through mx0 / mx1.
+template <int D, bool WRITE_P>
+__device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, int valid0,
+                                                    int valid1, float c, bool first, OnlineState& st, float& mx0,
+                                                    float& mx1) {
+  uint32_t r[128];
+#pragma unroll
+  for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
+  tmem_ld_wait();
+  if (valid0 < 64 || valid1 < 64) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      if (i >= valid0) r[i] = __float_as_uint(-INFINITY);
+      if (i >= valid1) r[64 + i] = __float_as_uint(-INFINITY);
+    }
+  }
+  mx0 = __uint_as_float(r[0]);
+  mx1 = __uint_as_float(r[64]);
+#pragma unroll
+  for (int i = 1; i < 64; ++i) {
+    mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+    mx1 = fmaxf(mx1, __uint_as_float(r[64 + i]));
+  }
+  const float mx = fmaxf(mx0, mx1);
+  st.m_true = fmaxf(st.m_true, mx);
+  const float ms = mx * c;
+  const bool grow = ms > st.m_used + 8.0f;
+  if (__any_sync(0xffffffffu, grow)) {
+    const float alpha = grow ? ex2(st.m_used - ms) : 1.0f;
+    if (grow) st.m_used = ms;
+    st.l *= alpha;
+    if (WRITE_P && !first) {
+      // the accumulator is quiescent: the commit that published this score tile also covers the
+      // previous P*V product of the same query tile
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + cc * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st32(o_addr + cc * 32, o);
+      }
+    }
+  }
+  float sum0 = 0.f, sum1 = 0.f;
+  const float neg_m = -st.m_used;
+#pragma unroll
+  for (int i = 0; i < 128; i += 2) {
+    const float p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
+    const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+    sum0 += p0;
+    sum1 += p1;
+    if (WRITE_P) r[i >> 1] = pack_bf16(p0, p1);
+  }
+  st.l += sum0 + sum1;
+  if (WRITE_P) {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) tmem_st16(p_addr + cc * 16, *reinterpret_cast<uint32_t(*)[16]>(&r[cc * 16]));
+    tmem_st_wait();
+  }
+}
+
+// Probabilities from a precomputed log-sum-exp: p = 2^(s*c - t_row), t_row = m*c + log2(l).
+// No reductions.  A half with valid == 0 is not even read; its probabilities are zero.
+__device__ __forceinline__ void softmax_ml_step(uint32_t s_addr, uint32_t p_addr, int valid0, int valid1, float c,
+                                                float t_row) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int valid = half ? valid1 : valid0;
+    uint32_t pk[32];
+    if (valid > 0) {                                   // warp-uniform
+      uint32_t r[64];
+      tmem_ld32(s_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_ld32(s_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) {
+        float p0 = ex2(fmaf(__uint_as_float(r[i]), c, -t_row));
+        float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, -t_row));
+        if (valid < 64) {
+          if (i >= valid) p0 = 0.f;
+          if (i + 1 >= valid) p1 = 0.f;
+        }
+        pk[i >> 1] = pack_bf16(p0, p1);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) pk[i] = 0u;
+    }
+    tmem_st32(p_addr + half * 32, pk);
+  }
+  tmem_st_wait();
+}
+
+// Write one row of the fp32 accumulator (D columns at o_addr) as bf16, scaled by `inv`.
+template <int D>
+__device__ __forceinline__ void store_o_row(uint32_t o_addr, __nv_bfloat16* orow, float inv, bool in_range) {
+#pragma unroll
+  for (int cc = 0; cc < D / 32; ++cc) {
+    uint32_t o[32];
+    tmem_ld32(o_addr + cc * 32, o);
+    tmem_ld_wait();
+    if (in_range) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+        v.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+        v.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+        v.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+        *reinterpret_cast<uint4*>(orow + cc * 32 + i * 8) = v;
+      }
+    }
+  }
+}
+
+}  // namespace fg

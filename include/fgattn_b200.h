@@ -1,0 +1,133 @@
+/* C ABI of libfgattn_b200: fine-grained threshold block-sparse attention forward path for B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the given CUDA stream
+ * and returns an fgattn_status (0 = ok) without synchronising.  Nothing here allocates or frees
+ * device memory except a 4-byte per-device error word on first use; scratch memory is passed in by
+ * the caller.  Citations name the interface of sankeerth95/fgattn_tk_cuda that each entry point
+ * replaces (paths inside that project).
+ *
+ * Conventions (python/extension.cpp:52-73, python/spattn/sparseattn_functionals.py:10-26):
+ *   q, k, v, o : bf16, [B, H, S, D] contiguous, 16-byte aligned, D in {64, 128}
+ *   max_q, denom : fp32 [B, H, 1, S_pad], S_pad = ceil(S/128)*128; tail max = 0, tail denom = -inf
+ *   kv_seq_len : number of leading key/value rows that take part (1..S); the reference hard-codes
+ *                this per shape (python/cuda_attn.cu:28-31), here it is a run-time argument
+ *   scale      : softmax scale; pass 0 for 1/sqrt(D) (the reference hard-codes 1/sqrt(128),
+ *                include/fullattn_tma.cuh:182-183)
+ *   stream     : a cudaStream_t (may be NULL for the default stream)
+ */
+#ifndef FGATTN_B200_H_
+#define FGATTN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FGATTN_OK = 0,
+  FGATTN_INVALID_ARGUMENT = 1,   /* null pointer, non-positive size, kv_seq_len out of range ... */
+  FGATTN_UNSUPPORTED = 2,        /* head dimension other than 64 / 128, list too long ...          */
+  FGATTN_MISALIGNED = 3,         /* a tensor base address is not 16-byte aligned                    */
+  FGATTN_CUDA_ERROR = 4,         /* a CUDA runtime / launch error; see fgattn_last_cuda_error       */
+  FGATTN_NO_DRIVER = 5,          /* the tensor-map encoder of the CUDA driver could not be found    */
+  FGATTN_DEVICE_TIMEOUT = 6,     /* a bounded in-kernel wait ran out (reported by fgattn_check)     */
+  FGATTN_SCRATCH_TOO_SMALL = 7
+} fgattn_status;
+
+const char* fgattn_status_string(int status);
+/* cudaError_t of the most recent FGATTN_CUDA_ERROR on this thread. */
+int fgattn_last_cuda_error(void);
+/* Synchronise `stream` and report whether any kernel launched through this library on the current
+ * device gave up on a bounded wait.  Returns FGATTN_OK or FGATTN_DEVICE_TIMEOUT; *code (optional)
+ * receives the id of the wait that ran out.  Clears the error word. */
+int fgattn_check(void* stream, int* code);
+
+/* Dense attention o = softmax(q k^T * scale) v.
+ * Replaces attn_fwd_wg_impl (python/extension.cpp:4-7, python/cuda_attn.cu:9-38), i.e. the
+ * full_attn operator (python/extension.cpp:52-73). */
+int fgattn_full_attn(void* o, const void* q, const void* k, const void* v, int batch, int heads, int seq, int D,
+                     int kv_seq_len, float scale, void* stream);
+
+/* Dense attention that also emits the per-row raw maximum and softmax denominator.
+ * Replaces attn_maxq_denom_impl (python/extension.cpp:22-27, python/cuda_attn.cu:97-139), the
+ * fullattn_maxq_denom operator (python/extension.cpp:178-204). */
+int fgattn_fullattn_maxq_denom(void* o, float* max_q, float* denom, const void* q, const void* k, const void* v,
+                               int batch, int heads, int seq, int D, int kv_seq_len, float scale, void* stream);
+
+/* Per-row raw maximum m_i = max_j q_i.k_j and denominator l_i = sum_j exp((q_i.k_j - m_i)*scale).
+ * Replaces maxq_denom_impl (python/extension.cpp:29-33, python/cuda_attn.cu:142-180), the
+ * maxq_denom operator (python/extension.cpp:226-248). */
+int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, int batch, int heads, int seq, int D,
+                      int kv_seq_len, float scale, void* stream);
+
+/* Threshold mask at the reference granularity: booleanmask[b,h,qblk,j] (int32,
+ * [B,H,ceil(S/128),mask_stride]) becomes 1 where some row of the 128-row query block has softmax
+ * probability > threshold for key token j; other entries are set to 0 (the whole tensor is
+ * cleared first, so pre-zeroing by the caller is harmless but not needed).
+ * Replaces booleanmask_128_impl (python/extension.cpp:36-41, python/cuda_attn.cu:183-266), the
+ * booleanmask_128 operator (python/extension.cpp:271-297). */
+int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
+                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_seq_len,
+                           float scale, void* stream);
+
+/* Mask rows -> ascending index lists: for every (b,h,seqblock) row of booleanmask
+ * ([B,H,seqblocks,mask_stride] int32, > 0 = keep) write the kept columns < seq in ascending order
+ * to kv_indices, fill the remaining slots with mask_stride and write the count.
+ * Replaces booleanmask_to_indexmask_impl (python/extension.cpp:44-49, python/cuda_attn.cu:269-303;
+ * kernel include/mask_utils.cuh:273-302, whose list order was nondeterministic). */
+int fgattn_booleanmask_to_indexmask(int* kv_indices, int* kv_num_indices, const int* booleanmask, int batch, int heads,
+                                    int seq, int seqblocks, int mask_stride, void* stream);
+
+/* Identity lists: kv_indices[b,h,sb,s] = s for all s < index_stride, kv_num_indices = seq.
+ * Replaces allindex_mask_impl (python/extension.cpp:16-19, python/cuda_attn.cu:78-94). */
+int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int heads, int seqblocks, int seq,
+                          int index_stride, void* stream);
+
+/* Sparse attention over key-TOKEN lists at the reference granularity: for each 128-row query
+ * block, softmax restricted to the listed key tokens (renormalised), times the listed v rows.
+ * kv_indices int32 [B,H,ceil(S/128),mask_stride], kv_num_indices int32 [B,H,ceil(S/128)].
+ * Replaces attn_sparse_fwd_wg_impl (python/extension.cpp:10-14, python/cuda_attn.cu:41-75), the
+ * sp_attn operator (python/extension.cpp:125-154). */
+int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
+                   const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, float scale,
+                   void* stream);
+
+/* ---- 64x64 block granularity --------------------------------------------------------------- */
+
+/* Bytes of scratch that fgattn_block_index_lists wants in order to process all batch*heads units
+ * in one pass (it works with less, down to one unit's worth, by looping over head chunks). */
+size_t fgattn_block_scratch_bytes(int batch, int heads, int seq, int kv_seq_len);
+
+/* One pass over all keys that produces max_q / denom (and, when o and v are non-null, the dense
+ * attention output) and from them the per-query-block key-BLOCK lists: block (qb, kb) of 64x64 is
+ * kept iff its largest softmax probability exceeds threshold (strict).  kb_indices int32
+ * [B,H,nqb,list_stride] receives ascending block indices, unused slots = nkb; kb_counts int32
+ * [B,H,nqb].  nqb = ceil(S/64), nkb = ceil(kv_seq_len/64), list_stride >= nkb.
+ * Fuses what the reference does as maxq_denom / fullattn_maxq_denom + booleanmask_128 +
+ * booleanmask_to_indexmask (python/spattn/mask_utils.py:306-334, :358-382) for the block
+ * granularity, without the second Q K^T pass of include/mask_utils.cuh:131-243. */
+int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, float* max_q, float* denom, void* o,
+                             const void* q, const void* k, const void* v, float threshold, int batch, int heads,
+                             int seq, int D, int kv_seq_len, float scale, void* scratch, size_t scratch_bytes,
+                             void* stream);
+
+/* Block-sparse attention with the precomputed (max_q, denom) of the softmax over ALL keys: rows
+ * of query block qb attend to the listed key blocks only, probabilities are not renormalised
+ * (the masked attention of python/test_mask.py:37-54).  The gather of K/V tiles by index replaces
+ * include/sparseattn_asyncgatherload_padded.cuh:130-256 and include/asyncloadutils.cuh:73-153. */
+int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                             const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
+                             int heads, int seq, int D, int kv_seq_len, float scale, void* stream);
+
+/* Same gather kernel with the renormalising softmax of the sp_attn operator (softmax over the kept
+ * keys only, include/sparseattn_asyncgatherload_padded.cuh:198-249) on key-block lists. */
+int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                          const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_seq_len,
+                          float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FGATTN_B200_H_ */

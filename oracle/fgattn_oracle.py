@@ -23,7 +23,7 @@ import torch
 
 __all__ = [
     "maxq_denom", "full_attn", "attnmapor", "boolean_to_index_mask_2d", "bitmask_to_indexmask",
-    "qk_bitmask", "qk_indexmask", "qk_block_pmax", "qk_block_bitmask", "qk_block_indexmask",
+    "qk_bitmask", "qk_token_pmax", "qk_indexmask", "qk_block_pmax", "qk_block_bitmask", "qk_block_indexmask",
     "qkattn_masked", "block_masked_attn", "sp_attn_tokens", "sp_attn_blocks", "allindex_mask",
     "near_threshold",
 ]
@@ -160,6 +160,26 @@ def qk_bitmask(q, k, thresh: float = 0.001, blocksz: int = 128, kv_seq_len: Opti
             for r0, r1 in _row_chunks(S, blocksz):
                 p = _head_probs_rows(q[b, h], kh, r0, r1, scale)
                 out[b, h, r0 // blocksz:(r1 + blocksz - 1) // blocksz] = attnmapor(p > thresh, blocksz)
+    return out
+
+
+def qk_token_pmax(q, k, blocksz: int = 128, kv_seq_len: Optional[int] = None,
+                  scale: Optional[float] = None) -> torch.Tensor:
+    """fp32 [B, H, ceil(S/blocksz), N]: for each query block and key token the largest softmax
+    probability over the block's rows (attnmapor of the float map, python/spattn/mask_utils.py:126-142);
+    qk_bitmask is this map compared with the threshold."""
+    q, k = _f32(q), _f32(k)
+    B, H, S, D = q.shape
+    n_kv = k.shape[2] if kv_seq_len is None else kv_seq_len
+    scale = (1.0 / math.sqrt(D)) if scale is None else scale
+    nqb = (S + blocksz - 1) // blocksz
+    out = torch.zeros(B, H, nqb, n_kv, dtype=torch.float32)
+    for b in range(B):
+        for h in range(H):
+            kh = k[b, h, :n_kv]
+            for r0, r1 in _row_chunks(S, blocksz):
+                p = _head_probs_rows(q[b, h], kh, r0, r1, scale)
+                out[b, h, r0 // blocksz:(r1 + blocksz - 1) // blocksz] = attnmapor(p, blocksz)
     return out
 
 
