@@ -8,6 +8,7 @@
 #include "dense_attn.cuh"
 #include "mask_kernels.cuh"
 #include "sparse_attn.cuh"
+#include "sparse_token_attn.cuh"
 #include "tensor_map.h"
 
 namespace {
@@ -276,9 +277,41 @@ int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int h
 int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
                    const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, float scale,
                    void* stream) {
-  (void)o; (void)q; (void)k; (void)v; (void)kv_indices; (void)kv_num_indices; (void)mask_stride;
-  (void)batch; (void)heads; (void)seq; (void)D; (void)scale; (void)stream;
-  return FGATTN_UNSUPPORTED;
+  int r = check_qk(q, k, batch, heads, seq, D, seq);
+  if (r) return r;
+  if (!o || !v || !kv_indices || !kv_num_indices || mask_stride < 1) return FGATTN_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(v)) return FGATTN_MISALIGNED;
+  fg::TokenParams p;
+  memset(&p, 0, sizeof(p));
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.kv_idx = kv_indices;
+  p.kv_cnt = kv_num_indices;
+  p.S = seq;
+  p.nqb = (seq + 127) / 128;
+  p.mask_stride = mask_stride;
+  p.scale_log2 = resolve_scale_log2(scale, D);
+  r = get_err_word(&p.err);
+  if (r) return r;
+  CUtensorMap mq;
+  if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128))
+    return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
+  dim3 grid((seq + 255) / 256, batch * heads, 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 128) {
+    auto kern = fg::sparse_token_attn_kernel<128>;
+    r = set_smem(kern, fg::TokenCfg<128>::kSmemBytes);
+    if (r) return r;
+    kern<<<grid, 384, fg::TokenCfg<128>::kSmemBytes, st>>>(mq, p);
+  } else {
+    auto kern = fg::sparse_token_attn_kernel<64>;
+    r = set_smem(kern, fg::TokenCfg<64>::kSmemBytes);
+    if (r) return r;
+    kern<<<grid, 384, fg::TokenCfg<64>::kSmemBytes, st>>>(mq, p);
+  }
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
 }
 
 size_t fgattn_block_scratch_bytes(int batch, int heads, int seq, int kv_seq_len) {

@@ -32,10 +32,11 @@ __device__ __forceinline__ void mask_cols(uint32_t (&r)[N], int valid) {
 //   p_addr : where the 64 packed-bf16 probability columns go (WRITE_P)
 //   o_addr : the row's D fp32 output accumulator columns (rescaled in place when the maximum grows)
 // Returns the raw maxima of the two 64-key halves through mx0 / mx1.
+//   colmask: optional 128-bit column mask (4 words, bit set = live column) applied on top
 template <int D, bool WRITE_P>
 __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, int valid0,
                                                     int valid1, float c, bool first, OnlineState& st, float& mx0,
-                                                    float& mx1) {
+                                                    float& mx1, const uint32_t* colmask = nullptr) {
   uint32_t r[128];
 #pragma unroll
   for (int cc = 0; cc < 4; ++cc) tmem_ld32(s_addr + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
@@ -45,6 +46,17 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
     for (int i = 0; i < 64; ++i) {
       if (i >= valid0) r[i] = __float_as_uint(-INFINITY);
       if (i >= valid1) r[64 + i] = __float_as_uint(-INFINITY);
+    }
+  }
+  if (colmask != nullptr) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint32_t mw = colmask[w];
+      if (mw != 0xffffffffu) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (!((mw >> i) & 1u)) r[w * 32 + i] = __float_as_uint(-INFINITY);
+      }
     }
   }
   mx0 = __uint_as_float(r[0]);

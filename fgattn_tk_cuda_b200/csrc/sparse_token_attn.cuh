@@ -1,0 +1,256 @@
+// Sparse attention over key-TOKEN lists at the reference granularity (128-row query blocks).
+// For each query block the listed K/V rows are gathered 128 at a time into swizzled shared-memory
+// tiles (16-byte cp.async per chunk, three gather warps), and the flash-attention step over the
+// gathered keys runs on tcgen05 with an online (renormalising) softmax.  A CTA runs two query
+// blocks ("slots") against one tensor pipe; their K/V tiles share one ring in consumption order.
+// List entries >= the number of key rows, and slots past the count, are masked out.
+#pragma once
+#include "sm100_ptx.cuh"
+#include "softmax_steps.cuh"
+
+namespace fg {
+
+struct TokenParams {
+  __nv_bfloat16* o;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const int* kv_idx;        // [BH, nqb128, mask_stride]
+  const int* kv_cnt;        // [BH, nqb128]
+  int* err;
+  int S, nqb, mask_stride;
+  float scale_log2;
+};
+
+template <int D>
+struct TokenCfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kGatherThreads = 96;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffRing = 2 * kTileBytes;
+  static constexpr int kOffBar = kOffRing + kStages * kTileBytes;
+  static constexpr int kSmemBytes = kOffBar + 1024 + 1024;
+};
+
+enum : int { TB_Q_FULL = 0, TB_FULL = 1, TB_EMPTY = 9, TB_S_FULL = 17, TB_P_FULL = 19, TB_O_FULL = 21, TB_COUNT = 23 };
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenParams p) {
+  using Cfg = TokenCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bars = sbase + Cfg::kOffBar;
+  auto bar = [&](int i) -> uint32_t { return bars + 8u * uint32_t(i); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffBar + 8 * TB_COUNT);
+  AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * TB_COUNT + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int q0 = blockIdx.x * 256;
+
+  if (tid == 0) {
+    ab->flag = 0;
+    mbar_init(bar(TB_Q_FULL), 1);
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(bar(TB_FULL + s), Cfg::kGatherThreads);
+      mbar_init(bar(TB_EMPTY + s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(TB_S_FULL + t), 1);
+      mbar_init(bar(TB_P_FULL + t), 128);
+      mbar_init(bar(TB_O_FULL + t), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  // per-slot list and number of 128-token steps
+  int cnt[2], nst[2];
+  const int* lst[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qb = (q0 >> 7) + t;
+    cnt[t] = 0;
+    lst[t] = p.kv_idx;
+    if (qb < p.nqb) {
+      cnt[t] = max(0, min(p.kv_cnt[size_t(bh) * p.nqb + qb], p.mask_stride));
+      lst[t] = p.kv_idx + (size_t(bh) * p.nqb + qb) * p.mask_stride;
+    }
+    nst[t] = (cnt[t] + 127) >> 7;
+  }
+  const int n_max = max(nst[0], nst[1]);
+
+  if (warp == 8 || warp >= 10) {
+    // ------------------------------------------------------------------ gather producers
+    reg_dealloc<72>();
+    if (warp == 8 && lane == 0) {
+      tma_prefetch_desc(&mq);
+      mbar_arrive_expect_tx(bar(TB_Q_FULL), 2 * Cfg::kTileBytes);
+      for (int t = 0; t < 2; ++t)
+        for (int h = 0; h < Cfg::kHalves; ++h)
+          tma_load_3d(sbase + Cfg::kOffQ + t * Cfg::kTileBytes + h * 16384, &mq, bar(TB_Q_FULL), h * 64, q0 + t * 128,
+                      bh);
+    }
+    __syncwarp();
+    const int gtid = (warp == 8) ? lane : (warp - 9) * 32 + lane;     // 0..95
+    constexpr int kChunksPerRow = D / 8;                               // 16-byte chunks per row
+    int idx = 0;
+    bool ok = true;
+    int pending_stage = -1;                                            // tile whose copies are in flight
+    auto gather_tile = [&](const __nv_bfloat16* base, int t, int j) {
+      const int st = idx % Cfg::kStages, f = idx / Cfg::kStages;
+      if (f > 0) ok = mbar_wait(bar(TB_EMPTY + st), (f - 1) & 1, ab, p.err, 701);
+      if (!ok) return;
+      const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+      for (int c = gtid; c < 128 * kChunksPerRow; c += Cfg::kGatherThreads) {
+        const int row = c / kChunksPerRow, ch = c % kChunksPerRow;
+        const int pos = j * 128 + row;
+        int tok = (pos < cnt[t]) ? lst[t][pos] : 0;
+        if (tok < 0 || tok >= p.S) tok = 0;                            // masked column: any finite row will do
+        const __nv_bfloat16* src = base + (size_t(bh) * p.S + tok) * D + ch * 8;
+        cp_async_16(dst + (ch >> 3) * 16384 + sw128_offset(row, ch & 7), src);
+      }
+      cp_async_commit();
+      if (pending_stage >= 0) {
+        cp_async_wait<1>();                                            // the previous tile has landed
+        fence_proxy_async_smem();
+        mbar_arrive(bar(TB_FULL + pending_stage));
+      }
+      pending_stage = st;
+      ++idx;
+    };
+    if (nst[0] > 0) gather_tile(p.k, 0, 0);
+    if (nst[1] > 0 && ok) gather_tile(p.k, 1, 0);
+    for (int j = 0; j < n_max && ok; ++j) {
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j < nst[t]) {
+          gather_tile(p.v, t, j);
+          if (ok && j + 1 < nst[t]) gather_tile(p.k, t, j + 1);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    if (ok && pending_stage >= 0) {
+      fence_proxy_async_smem();
+      mbar_arrive(bar(TB_FULL + pending_stage));
+    }
+    if (!ok && warp == 8 && lane == 0) mbar_wait_brief(bar(TB_Q_FULL), 0);
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ UMMA issuer
+    reg_dealloc<72>();
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
+      const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
+      int idx = 0;
+      bool ok = mbar_wait(bar(TB_Q_FULL), 0, ab, p.err, 801);
+      auto qk = [&](int t) {
+        const int st = idx % Cfg::kStages;
+        ok = mbar_wait(bar(TB_FULL + st), (idx / Cfg::kStages) & 1, ab, p.err, 802);
+        if (!ok) return;
+        tc_fence_after();
+        const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_ss(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                  idesc_qk, ks > 0);
+        }
+        umma_commit(bar(TB_S_FULL + t));
+        umma_commit(bar(TB_EMPTY + st));
+        ++idx;
+      };
+      auto pv = [&](int t, int j) {
+        const int st = idx % Cfg::kStages;
+        ok = mbar_wait(bar(TB_FULL + st), (idx / Cfg::kStages) & 1, ab, p.err, 803);
+        if (ok) ok = mbar_wait(bar(TB_P_FULL + t), j & 1, ab, p.err, 804);
+        if (!ok) return;
+        tc_fence_after();
+        const uint32_t va = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(bar(TB_EMPTY + st));
+        ++idx;
+      };
+      if (ok && nst[0] > 0) qk(0);
+      if (ok && nst[1] > 0) qk(1);
+      for (int j = 0; j < n_max && ok; ++j) {
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < nst[t]) {
+            pv(t, j);
+            if (!ok) break;
+            if (j + 1 < nst[t]) qk(t);
+            else umma_commit(bar(TB_O_FULL + t));
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    reg_alloc<216>();
+    const int t = warp >> 2, wq = warp & 3;
+    const int row = q0 + t * 128 + wq * 32 + lane;
+    const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
+    const uint32_t s_addr = lane_base + t * 128, o_addr = lane_base + 256 + t * 128;
+    OnlineState st;
+    online_init(st);
+    bool ok = true;
+    for (int j = 0; j < nst[t]; ++j) {
+      // which of the step's 128 gathered columns are real keys
+      uint32_t live[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const int pos = j * 128 + w * 32 + lane;
+        const int tok = (pos < cnt[t]) ? lst[t][pos] : -1;
+        live[w] = __ballot_sync(0xffffffffu, tok >= 0 && tok < p.S);
+      }
+      ok = mbar_wait(bar(TB_S_FULL + t), j & 1, ab, p.err, 901);
+      if (!ok) break;
+      tc_fence_after();
+      float mx0, mx1;
+      softmax_online_step<D, true>(s_addr, s_addr, o_addr, 64, 64, p.scale_log2, j == 0, st, mx0, mx1, live);
+      tc_fence_before();
+      mbar_arrive(bar(TB_P_FULL + t));
+    }
+    __nv_bfloat16* orow = p.o + (size_t(bh) * p.S + row) * D;
+    if (nst[t] == 0) {
+      if (row < p.S) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+      }
+    } else if (ok) {
+      ok = mbar_wait(bar(TB_O_FULL + t), 0, ab, p.err, 902);
+      if (ok) {
+        tc_fence_after();
+        store_o_row<D>(o_addr, orow, st.l > 0.f ? 1.0f / st.l : 0.f, row < p.S);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace fg

@@ -1,0 +1,200 @@
+"""Mask pipeline wrappers and mask caches, mirroring python/spattn/mask_utils.py of the reference.
+
+`blocksz=128` keeps the reference's granularity (128 query rows x 1 key token, token lists);
+`blocksz=64` is the 64x64 block mode: key-BLOCK lists plus the per-row (max_q, denom) that the
+block-sparse kernel needs, produced in ONE pass over the keys.
+
+The reference's pure-PyTorch functions of the same module (qk_bitmask, qk_indexmask, attnmapor,
+boolean_to_index_mask_2d, bitmask_to_indexmask) are its CPU path; they are deliberately not part of
+this package (no CPU route exists here) and live, restated, in the test oracle.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import cuda_attn  # noqa: F401  registers torch.ops.cuda_attn
+
+spattn_interface = torch.ops.cuda_attn
+
+
+def _pad128(n: int) -> int:
+    return 128 * ((n + 127) // 128)
+
+
+# ------------------------------------------------------------------------------------------------
+# mask caches (python/spattn/mask_utils.py:17-98): decide on which diffusion runs the mask is
+# rebuilt and hand the cached lists to the sparse steps in between
+# ------------------------------------------------------------------------------------------------
+class NaiveMaskCache:
+    """Keeps whatever the build step produced, per layer, on the device."""
+
+    def __init__(self, compute_cache_at):
+        self.cache = {}
+        self.compute_cache_at = compute_cache_at
+
+    def run_fullattn(self, ditrun) -> bool:
+        return ditrun in self.compute_cache_at
+
+    def get_mask_from_cache(self, layer):
+        return self.cache[layer]
+
+    def update_cache(self, layer, *mask):
+        self.cache[layer] = tuple(mask)
+
+
+class OffloadMaskCache(NaiveMaskCache):
+    """Index lists live in host memory between uses; counts (and m/l in block mode) stay on the GPU."""
+
+    def get_mask_from_cache(self, layer, ditrun=0):
+        first, *rest = self.cache[layer]
+        return (first.to("cuda", non_blocking=True), *rest)
+
+    def update_cache(self, layer, first, *rest):
+        self.cache[layer] = (first.cpu(), *rest)
+
+
+class BitMaskCache(NaiveMaskCache):
+    """Stores the int mask [B,H,SB,stride] and rebuilds the lists on every read."""
+
+    def get_mask_from_cache(self, layer):
+        mask, seq_len = self.cache[layer]
+        return bitmask_to_indexmask_cuda(mask, seq_len)
+
+    def update_cache(self, layer, mask, seq_len):
+        self.cache[layer] = (mask, seq_len)
+
+
+class CompressedBitMaskCache(BitMaskCache):
+    """Same, with the mask packed to one bit per entry (pack / unpack below)."""
+
+    def get_mask_from_cache(self, layer):
+        packed, seq_len = self.cache[layer]
+        return bitmask_to_indexmask_cuda(unpack(packed).to(torch.int32), seq_len)
+
+    def update_cache(self, layer, mask, seq_len):
+        self.cache[layer] = (pack(mask > 0), seq_len)
+
+
+def pack(bool_tensor: torch.Tensor) -> torch.Tensor:
+    """bool [..., W] (W % 8 == 0) -> uint8 [..., W/8], least significant bit first
+    (python/spattn/mask_utils.py:421-430)."""
+    w = torch.tensor([1, 2, 4, 8, 16, 32, 64, 128], dtype=torch.uint8, device=bool_tensor.device)
+    g = bool_tensor.reshape(*bool_tensor.shape[:-1], bool_tensor.shape[-1] // 8, 8).to(torch.uint8)
+    return (g * w).sum(dim=-1).to(torch.uint8)
+
+
+def unpack(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of pack (python/spattn/mask_utils.py:433-440)."""
+    w = torch.tensor([1, 2, 4, 8, 16, 32, 64, 128], dtype=torch.uint8, device=packed.device)
+    bits = (packed.unsqueeze(-1) & w) != 0
+    return bits.reshape(*packed.shape[:-1], packed.shape[-1] * 8)
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic lists (python/spattn/mask_utils.py:175-203)
+# ------------------------------------------------------------------------------------------------
+def allindex_mask(B: int, H: int, max_stride: int, S: int, BLOCKSZ: int, device="cuda"):
+    nb = (S + BLOCKSZ - 1) // BLOCKSZ
+    kv_indices = torch.empty(B, H, nb, max_stride, device=device, dtype=torch.int32)
+    kv_num_indices = torch.empty(B, H, nb, device=device, dtype=torch.int32)
+    spattn_interface.all_index_mask(kv_indices, kv_num_indices, B, H, nb, S)
+    return kv_indices, kv_num_indices
+
+
+def halfindex_mask(B: int, H: int, S: int, BLOCKSZ: int, device="cuda"):
+    nb = (S + BLOCKSZ - 1) // BLOCKSZ
+    idx = (2 * torch.arange(S // 2, device=device, dtype=torch.int32)).expand(B, H, nb, S // 2).contiguous()
+    return idx, torch.full((B, H, nb), S // 2, device=device, dtype=torch.int32)
+
+
+def allindex_randompermutation_mask(B: int, H: int, max_stride: int, S: int, BLOCKSZ: int, device="cuda"):
+    nb = (S + BLOCKSZ - 1) // BLOCKSZ
+    perm = torch.randperm(S, device=device).to(torch.int32)
+    if max_stride > S:
+        perm = torch.cat([perm, torch.full((max_stride - S,), max_stride, device=device, dtype=torch.int32)])
+    return perm.expand(B, H, nb, max_stride).contiguous(), torch.full((B, H, nb), S, device=device, dtype=torch.int32)
+
+
+# ------------------------------------------------------------------------------------------------
+# CUDA mask pipeline
+# ------------------------------------------------------------------------------------------------
+def _maxq_denom(q, k):
+    B, H, S, _ = q.shape
+    max_q = torch.empty((B, H, 1, _pad128(S)), dtype=torch.float32, device=q.device)
+    denom = torch.empty_like(max_q)
+    spattn_interface.maxq_denom(max_q, denom, q.contiguous(), k.contiguous())
+    return max_q, denom
+
+
+def qk_bitmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz=128):
+    """int32 [B,H,ceil(S/128),S_pad] token mask (python/spattn/mask_utils.py:337-354)."""
+    assert blocksz == 128
+    B, H, S, _ = q.shape
+    mask = torch.empty((B, H, (S + 127) // 128, max_q.shape[3]), device=q.device, dtype=torch.int32)
+    spattn_interface.booleanmask_128(mask, max_q.contiguous(), denom.contiguous(), q.contiguous(), k.contiguous(),
+                                     thresh)
+    return mask
+
+
+def qk_bitmask_cuda(q, k, thresh, blocksz=128):
+    """bool token mask (python/spattn/mask_utils.py:248-269)."""
+    max_q, denom = _maxq_denom(q, k)
+    return qk_bitmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz) > 0
+
+
+def bitmask_to_indexmask_cuda(booleanmask, seq=None):
+    """Mask -> ascending token lists + counts (python/spattn/mask_utils.py:293-303); `seq` bounds
+    the key index (default: the mask width)."""
+    B, H, SB, stride = booleanmask.shape
+    kv_indices = torch.empty((B, H, SB, stride), device=booleanmask.device, dtype=torch.int32)
+    num_kv_indices = torch.empty((B, H, SB), device=booleanmask.device, dtype=torch.int32)
+    spattn_interface.booleanmask_to_indexmask(kv_indices, num_kv_indices, booleanmask.to(torch.int32).contiguous(),
+                                              stride if seq is None else seq)
+    return kv_indices, num_kv_indices
+
+
+def qk_indexmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz=128):
+    """Token lists from an existing (max_q, denom) (python/spattn/mask_utils.py:358-382)."""
+    mask = qk_bitmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz)
+    return bitmask_to_indexmask_cuda(mask, q.shape[2])
+
+
+_scratch = {}
+
+
+def _block_scratch(q):
+    B, H, S, _ = q.shape
+    need = cuda_attn.block_scratch_bytes(B, H, S, S)
+    per_head = need // (B * H)
+    free, _total = torch.cuda.mem_get_info(q.device)
+    heads_fit = max(1, min(B * H, int(free * 0.5) // per_head))     # fewer heads -> the op loops over chunks
+    want = per_head * heads_fit
+    have = _scratch.get(q.device)
+    if have is None or have.numel() * 4 < want:
+        _scratch[q.device] = have = torch.empty(want // 4, dtype=torch.float32, device=q.device)
+    return have
+
+
+def qk_block_indexmask_cuda(q, k, thresh, v=None):
+    """64x64 block mode, one pass: returns (kb_indices [B,H,nqb,nkb], kb_counts [B,H,nqb], max_q,
+    denom) and, when v is given, the dense attention output as a fifth element."""
+    B, H, S, D = q.shape
+    nqb = nkb = (S + 63) // 64
+    kb_indices = torch.empty((B, H, nqb, nkb), device=q.device, dtype=torch.int32)
+    kb_counts = torch.empty((B, H, nqb), device=q.device, dtype=torch.int32)
+    max_q = torch.empty((B, H, 1, _pad128(S)), dtype=torch.float32, device=q.device)
+    denom = torch.empty_like(max_q)
+    o = torch.empty((B, H, S, D), device=q.device, dtype=torch.bfloat16) if v is not None else None
+    spattn_interface.block_index_lists(kb_indices, kb_counts, max_q, denom, o, q.contiguous(), k.contiguous(),
+                                       None if v is None else v.contiguous(), thresh, _block_scratch(q))
+    return (kb_indices, kb_counts, max_q, denom) + ((o,) if v is not None else ())
+
+
+def qk_indexmask_cuda(q, k, thresh, blocksz=128):
+    """python/spattn/mask_utils.py:306-334.  blocksz=128: token lists; blocksz=64: see
+    qk_block_indexmask_cuda (returns four tensors)."""
+    if blocksz == 64:
+        return qk_block_indexmask_cuda(q, k, thresh)
+    assert blocksz == 128
+    max_q, denom = _maxq_denom(q, k)
+    return qk_indexmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz)

@@ -1,0 +1,100 @@
+"""Model-facing attention entry points, mirroring python/spattn/sparseattn_functionals.py of the
+reference: same names, same `(query, key, value, current_layer, ditrun, **kwargs)` calling
+convention, same kwargs (`thresh`, `blocksz`, `mask_cache`).  `blocksz=128` runs the reference
+granularity (token lists, renormalising sp_attn); `blocksz=64` runs the 64x64 block mode (key-block
+lists, probabilities from the full softmax's max_q / denom)."""
+from __future__ import annotations
+
+import torch
+
+from . import mask_utils
+
+spattn_interface = torch.ops.cuda_attn
+
+
+def _out(query):
+    return torch.empty(query.shape, device=query.device, dtype=torch.bfloat16)
+
+
+def _ml(query):
+    B, H, S, _ = query.shape
+    m = torch.empty((B, H, 1, 128 * ((S + 127) // 128)), dtype=torch.float32, device=query.device)
+    return m, torch.empty_like(m)
+
+
+def baseline_attn(query, key, value, current_layer=None, ditrun=None, *args, **kwargs):
+    """Dense attention (sparseattn_functionals.py:10-15)."""
+    out = _out(query)
+    spattn_interface.full_attn(out, query.contiguous(), key.contiguous(), value.contiguous())
+    return out
+
+
+def baseline_attn_maxq_denom(query, key, value, current_layer=None, ditrun=None, *args, **kwargs):
+    """Dense attention that also computes max_q / denom (sparseattn_functionals.py:18-26)."""
+    out = _out(query)
+    max_q, denom = _ml(query)
+    spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(), value.contiguous())
+    return out
+
+
+def _sparse(out, query, key, value, mask):
+    q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
+    if len(mask) == 4:                                    # block mode: (kb_indices, kb_counts, max_q, denom)
+        spattn_interface.sp_attn_blocks_ml(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2], mask[3])
+    else:                                                 # token lists
+        spattn_interface.sp_attn(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
+    return out
+
+
+def attn_computed_with_sparse_mask_cuda(query, key, value, *args, **kwargs):
+    """Build the mask from (query, key) and run the sparse kernel with it
+    (sparseattn_functionals.py:61-69)."""
+    mask = mask_utils.qk_indexmask_cuda(query, key, kwargs["thresh"], blocksz=kwargs["blocksz"])
+    return _sparse(_out(query), query, key, value, mask)
+
+
+def compute_cache_and_attn_cuda(query, key, value, *args, **kwargs):
+    """Dense attention + mask in one go (sparseattn_functionals.py:74-84).  Returns
+    (out, kv_indices, kv_num_indices) and, in block mode, additionally (max_q, denom)."""
+    thresh, blocksz = kwargs["thresh"], kwargs["blocksz"]
+    if blocksz == 64:
+        idx, cnt, max_q, denom, out = mask_utils.qk_block_indexmask_cuda(query, key, thresh, v=value)
+        return out, idx, cnt, max_q, denom
+    out = _out(query)
+    max_q, denom = _ml(query)
+    spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(), value.contiguous())
+    idx, cnt = mask_utils.qk_indexmask_from_maxq_denom_cuda(max_q, denom, query, key, thresh, blocksz=blocksz)
+    return out, idx, cnt
+
+
+def sparse_attn_from_cache_cuda(query, key, value, *args, **kwargs):
+    """Sparse step from a cached mask (sparseattn_functionals.py:87-93)."""
+    mask = kwargs["mask_cache"].get_mask_from_cache(kwargs.get("current_layer", 0))
+    return _sparse(_out(query), query, key, value, mask)
+
+
+def cached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
+    """Dense + mask build on the runs the cache names, sparse from the cache otherwise
+    (sparseattn_functionals.py:95-113)."""
+    mask_cache = kwargs["mask_cache"]
+    if mask_cache.run_fullattn(ditrun):
+        out, *mask = compute_cache_and_attn_cuda(query, key, value, thresh=kwargs["thresh"], blocksz=kwargs["blocksz"])
+        mask_cache.update_cache(current_layer, *mask)
+        return out
+    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer))
+
+
+def bitmaskcached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
+    """Like cached_attn_cuda with the int mask cached instead of the lists
+    (sparseattn_functionals.py:116-134); reference granularity only."""
+    mask_cache = kwargs["mask_cache"]
+    if mask_cache.run_fullattn(ditrun):
+        out = _out(query)
+        max_q, denom = _ml(query)
+        spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(),
+                                             value.contiguous())
+        mask = mask_utils.qk_bitmask_from_maxq_denom_cuda(max_q, denom, query, key, kwargs["thresh"],
+                                                          blocksz=kwargs["blocksz"])
+        mask_cache.update_cache(current_layer, mask, query.shape[2])
+        return out
+    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer))
