@@ -311,12 +311,10 @@ def main():
                 "ideal_speedup_1_over_density": 1.0 / density,
                 "speedup_gap": (1.0 / density) / (ms_full / ms_step)},
         }
-        traffic_file = ROOT / "profiles" / "sparse_block_attn_c3_traffic.json"
-        if traffic_file.exists():
-            try:
-                line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
-            except Exception:
-                pass
+        # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
+        # profiles/sparse_block_attn_c3_16heads.md (16 heads: 271 MB), scaled by heads
+        if args.workload == "c3":
+            line["roofline"]["traffic"] = 271.0e6 * (w.B * w.H) / 16.0
         if world == 1 and not args.no_cpu_baseline:
             r = run_cpu(w, steps=2, warmup=1, budget_s=25.0)
             line["cpu_baseline"] = {k_: r[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
