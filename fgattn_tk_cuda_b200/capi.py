@@ -10,7 +10,10 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "libfgattn_b200.so"
+import os
+
+# FGATTN_B200_LIB overrides the library file (A/B builds of the same C ABI)
+_LIB_PATH = Path(os.environ.get("FGATTN_B200_LIB") or Path(__file__).resolve().parent / "libfgattn_b200.so")
 
 OK = 0
 STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "UNSUPPORTED", 3: "MISALIGNED", 4: "CUDA_ERROR", 5: "NO_DRIVER",
@@ -33,7 +36,9 @@ PROTOTYPES = {
     "fgattn_block_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f, _vp,
                                       _sz, _vp]),
-    "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz,
+                                      _vp]),
+    "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
     "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
 }
 
@@ -163,12 +168,19 @@ def block_index_lists(kb_indices, kb_counts, max_q, denom, q, k, threshold, scra
               _ptr(scratch), scratch.numel() * scratch.element_size(), _stream(q))
 
 
-def sp_attn_blocks_ml(o, q, k, v, kb_indices, kb_counts, max_q, denom, kv_seq_len=None, scale=0.0):
+def sp_attn_workspace_bytes(B, H, S) -> int:
+    return int(lib().fgattn_sp_attn_workspace_bytes(B, H, S))
+
+
+def sp_attn_blocks_ml(o, q, k, v, kb_indices, kb_counts, max_q, denom, kv_seq_len=None, scale=0.0, workspace=None):
     _check_qkv(o, q, k, v)
     B, H, S, D = q.shape
+    if workspace is None:                                # stream-ordered scratch from torch's caching allocator
+        workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn_blocks_ml", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
-              kb_indices.shape[3], _ptr(max_q), _ptr(denom), B, H, S, D, kv_seq_len or S, scale, _stream(q))
+              kb_indices.shape[3], _ptr(max_q), _ptr(denom), B, H, S, D, kv_seq_len or S, scale, _ptr(workspace),
+              workspace.numel() * workspace.element_size(), _stream(q))
 
 
 def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0):

@@ -152,7 +152,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   } else if (warp == 9) {
     // ------------------------------------------------------------------ UMMA issuer
     reg_dealloc<72>();
-    if (lane == 0) {
+    {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
       auto issue_qk = [&](int t, int kstage, uint32_t d_col) {
@@ -160,7 +160,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_ss(tmem + d_col, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+          umma_ss_elect(tmem + d_col, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
                   idesc_qk, ks > 0);
         }
       };
@@ -168,56 +168,56 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         const uint32_t va = sbase + Cfg::kOffV + vstage * Cfg::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)   // 128 keys, 16 per UMMA
-          umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+          umma_ts_elect(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
                   idesc_pv, (acc || ks > 0) ? 1u : 0u);
       };
-      bool ok = mbar_wait(bar(BAR_Q_FULL), 0, ab, p.err, 201);
+      bool ok = mbar_wait_warp(bar(BAR_Q_FULL), 0, ab, p.err, 201);
       if (HAS_V) {
-        if (ok) ok = mbar_wait(bar(BAR_K_FULL + 0), 0, ab, p.err, 202);
+        if (ok) ok = mbar_wait_warp(bar(BAR_K_FULL + 0), 0, ab, p.err, 202);
         if (ok) {
           tc_fence_after();
           for (int t = 0; t < 2; ++t) {
             issue_qk(t, 0, t * 128);
-            umma_commit(bar(BAR_S_FULL + t * 2));
+            umma_commit_elect(bar(BAR_S_FULL + t * 2));
           }
-          umma_commit(bar(BAR_K_EMPTY + 0));
+          umma_commit_elect(bar(BAR_K_EMPTY + 0));
         }
         for (int j = 0; j < n_tiles && ok; ++j) {
           const int vs = j % Cfg::kVStages;
-          ok = mbar_wait(bar(BAR_V_FULL + vs), (j / Cfg::kVStages) & 1, ab, p.err, 203);
+          ok = mbar_wait_warp(bar(BAR_V_FULL + vs), (j / Cfg::kVStages) & 1, ab, p.err, 203);
           const bool more = (j + 1 < n_tiles);
           const int ks = (j + 1) % Cfg::kKStages;
-          if (ok && more) ok = mbar_wait(bar(BAR_K_FULL + ks), ((j + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
+          if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((j + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
           for (int t = 0; t < 2 && ok; ++t) {
-            ok = mbar_wait(bar(BAR_P_FULL + t), j & 1, ab, p.err, 205);
+            ok = mbar_wait_warp(bar(BAR_P_FULL + t), j & 1, ab, p.err, 205);
             if (!ok) break;
             tc_fence_after();
             issue_pv(t, vs, j > 0);
             if (more) {
               issue_qk(t, ks, t * 128);
-              umma_commit(bar(BAR_S_FULL + t * 2));
+              umma_commit_elect(bar(BAR_S_FULL + t * 2));
             } else {
-              umma_commit(bar(BAR_O_FULL + t));
+              umma_commit_elect(bar(BAR_O_FULL + t));
             }
           }
           if (ok) {
-            umma_commit(bar(BAR_V_EMPTY + vs));
-            if (more) umma_commit(bar(BAR_K_EMPTY + ks));
+            umma_commit_elect(bar(BAR_V_EMPTY + vs));
+            if (more) umma_commit_elect(bar(BAR_K_EMPTY + ks));
           }
         }
       } else {
         // no V: S is double-buffered per query tile; tile t, buffer b lives at column (2t+b)*128
         for (int j = 0; j < n_tiles && ok; ++j) {
           const int ks = j % Cfg::kKStages, b = j & 1, f = j >> 1;
-          ok = mbar_wait(bar(BAR_K_FULL + ks), (j / Cfg::kKStages) & 1, ab, p.err, 206);
+          ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (j / Cfg::kKStages) & 1, ab, p.err, 206);
           for (int t = 0; t < 2 && ok; ++t) {
-            if (f > 0) ok = mbar_wait(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
+            if (f > 0) ok = mbar_wait_warp(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
             if (!ok) break;
             tc_fence_after();
             issue_qk(t, ks, (t * 2 + b) * 128);
-            umma_commit(bar(BAR_S_FULL + t * 2 + b));
+            umma_commit_elect(bar(BAR_S_FULL + t * 2 + b));
           }
-          if (ok) umma_commit(bar(BAR_K_EMPTY + ks));
+          if (ok) umma_commit_elect(bar(BAR_K_EMPTY + ks));
         }
       }
     }

@@ -122,10 +122,14 @@ void sp_attn_blocks_ml(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch:
   check_dtype(kb_indices, at::kInt, "kb_indices"); check_dtype(kb_counts, at::kInt, "kb_counts");
   check_dtype(max_q, at::kFloat, "max_q"); check_dtype(denom, at::kFloat, "denom");
   c10::cuda::CUDAGuard guard(q.device());
+  // work-queue scratch of the persistent kernel, from the stream-ordered caching allocator
+  const int64_t ws_bytes = int64_t(fgattn_sp_attn_workspace_bytes(q.size(0), q.size(1), q.size(2)));
+  torch::Tensor ws = torch::empty({ws_bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
   check_status(fgattn_sp_attn_blocks_ml(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                         kb_indices.data_ptr<int>(), kb_counts.data_ptr<int>(), int(kb_indices.size(3)),
                                         max_q.data_ptr<float>(), denom.data_ptr<float>(), q.size(0), q.size(1),
-                                        q.size(2), q.size(3), k.size(2), 0.f, stream_of(q)), "sp_attn_blocks_ml");
+                                        q.size(2), q.size(3), k.size(2), 0.f, ws.data_ptr(), size_t(ws_bytes),
+                                        stream_of(q)), "sp_attn_blocks_ml");
 }
 
 void sp_attn_blocks(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor kb_indices,

@@ -1,6 +1,7 @@
 // extern "C" entry points of libfgattn_b200: argument checks, TMA tensor maps, launches.
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdlib.h>
 #include <algorithm>
 #include <mutex>
 
@@ -8,6 +9,7 @@
 #include "dense_attn.cuh"
 #include "mask_kernels.cuh"
 #include "sparse_attn.cuh"
+#include "sparse_ml_persistent.cuh"
 #include "sparse_token_attn.cuh"
 #include "tensor_map.h"
 
@@ -357,11 +359,77 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
   return FGATTN_OK;
 }
 
+size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq) {
+  if (batch <= 0 || heads <= 0 || seq <= 0) return 0;
+  const size_t npairs = size_t((seq + 127) / 128);
+  return 16 + size_t(batch) * heads * npairs * sizeof(int);
+}
+
 int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                              const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
-                             int heads, int seq, int D, int kv_seq_len, float scale, void* stream) {
-  return launch_sparse<false>(o, q, k, v, kb_indices, kb_counts, list_stride, max_q, denom, batch, heads, seq, D,
-                              kv_seq_len, scale, static_cast<cudaStream_t>(stream));
+                             int heads, int seq, int D, int kv_seq_len, float scale, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  int r = check_qk(q, k, batch, heads, seq, D, kv_seq_len);
+  if (r) return r;
+  if (!o || !v || !kb_indices || !kb_counts || !max_q || !denom || !workspace || list_stride < 1)
+    return FGATTN_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(v) || !aligned16(workspace)) return FGATTN_MISALIGNED;
+  if (workspace_bytes < fgattn_sp_attn_workspace_bytes(batch, heads, seq)) return FGATTN_SCRATCH_TOO_SMALL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  fg::SparseMLParams p;
+  memset(&p, 0, sizeof(p));
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.max_q = max_q;
+  p.denom = denom;
+  p.kb_idx = kb_indices;
+  p.kb_cnt = kb_counts;
+  p.queue = static_cast<int*>(workspace);
+  p.order = static_cast<int*>(workspace) + 4;
+  p.S = seq;
+  p.S_pad = ((seq + 127) / 128) * 128;
+  p.kv_len = kv_seq_len;
+  p.nqb = (seq + 63) / 64;
+  p.nkb = (kv_seq_len + 63) / 64;
+  p.npairs = (seq + 127) / 128;
+  p.n_items = batch * heads * p.npairs;
+  p.list_stride = list_stride;
+  p.list_cap = p.nkb + 2;
+  p.scale_log2 = resolve_scale_log2(scale, D);
+  if (const char* dbg = getenv("FGATTN_DEBUG_SPARSE")) p.debug = atoi(dbg);
+  if ((p.debug & 8) && workspace_bytes >= fgattn_sp_attn_workspace_bytes(batch, heads, seq) + 256 * 32 * 8 + 64)
+    p.stats = reinterpret_cast<long long*>(static_cast<char*>(workspace) +
+                                           ((fgattn_sp_attn_workspace_bytes(batch, heads, seq) + 63) / 64) * 64);
+  r = get_err_word(&p.err);
+  if (r) return r;
+  CUtensorMap mq, mk, mv;
+  if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128) || fg::make_qkv_map(&mk, k, batch * heads, seq, D, 64) ||
+      fg::make_qkv_map(&mv, v, batch * heads, seq, D, 64))
+    return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
+  int dev = 0, sms = 0;
+  FG_CUDA(cudaGetDevice(&dev));
+  FG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (p.npairs * int(sizeof(int)) > 48 * 1024) return FGATTN_UNSUPPORTED;
+  fg::sparse_order_kernel<<<batch * heads, 256, p.npairs * sizeof(int), st>>>(kb_counts, static_cast<int*>(workspace) + 4,
+                                                                          p.queue, p.nqb, p.npairs);
+  FG_CUDA(cudaGetLastError());
+  const int grid = std::min(p.n_items, sms);
+  if (D == 128) {
+    const int smem = fg::SparseMLCfg<128>::smem_bytes(p.list_cap, p.nkb);
+    if (smem > 232448) return FGATTN_UNSUPPORTED;
+    auto kern = fg::sparse_ml_persistent_kernel<128>;
+    r = set_smem(kern, smem);
+    if (r) return r;
+    kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
+  } else {
+    const int smem = fg::SparseMLCfg<64>::smem_bytes(p.list_cap, p.nkb);
+    if (smem > 232448) return FGATTN_UNSUPPORTED;
+    auto kern = fg::sparse_ml_persistent_kernel<64>;
+    r = set_smem(kern, smem);
+    if (r) return r;
+    kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
+  }
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
 }
 
 int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,

@@ -8,6 +8,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifndef FG_WAIT_HINT_NS
+#define FG_WAIT_HINT_NS 2000
+#endif
+
 namespace fg {
 
 // ---------------------------------------------------------------------------------------------
@@ -57,10 +61,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef FG_SPIN_TEST_WAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.b32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds and
+// wakes as soon as the phase completes, so a waiting warp does not burn issue slots of the
+// sub-partition it shares with the math warps.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
@@ -89,6 +112,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, AbortSt
       }
     }
   }
+}
+
+// Whole-warp variant for warp-uniform control flow (the UMMA issuer): every lane polls, the verdict
+// is made uniform so that a following elect.sync sees a converged warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
+  const bool ok = mbar_wait(bar, parity, ab, err, code);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // Wait used only on the abort path: short budget, no error recording.
@@ -185,9 +215,25 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Issue from a converged warp: one elected lane executes the instruction.  Keeping the surrounding
+// loop warp-uniform lets the compiler hold descriptors in uniform registers, which halves the issue
+// cost of tcgen05.mma compared with a loop that runs under `if (lane == 0)`.
+__device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  if (elect_one()) umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  if (elect_one()) umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+}
+
 // mbarrier arrives once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
+  if (elect_one()) umma_commit(bar);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -246,6 +292,48 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed fp32 pairs (sm_100 f32x2 instructions): half the instruction count of scalar FFMA/FADD.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// 2^x for two values on the FMA pipe (no MUFU): round-to-nearest split x = n + f, f in [-0.5, 0.5],
+// cubic minimax polynomial for 2^f (max relative error 7.5e-5, far below bf16 resolution), n added
+// to the exponent field.  Inputs below -126 give ~1e-38.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& p0, float& p1) {
+  const float kMagic = 12582912.0f;                       // 1.5 * 2^23
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  const uint64_t x = f2_pack(x0, x1);
+  const uint64_t xr = f2_add(x, f2_pack(kMagic, kMagic));  // integer part in the low mantissa bits
+  const uint64_t xi = f2_add(xr, f2_pack(-kMagic, -kMagic));
+  const uint64_t f = f2_fma(xi, f2_pack(-1.0f, -1.0f), x);
+  uint64_t q = f2_fma(f, f2_pack(0.05517160892486572f, 0.05517160892486572f),
+                      f2_pack(0.2426111102104187f, 0.2426111102104187f));
+  q = f2_fma(q, f, f2_pack(0.6932609677314758f, 0.6932609677314758f));
+  q = f2_fma(q, f, f2_pack(0.9999280571937561f, 0.9999280571937561f));
+  float q0, q1, r0, r1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(xr, r0, r1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -202,39 +202,39 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
   } else if (warp == 9) {
     // ------------------------------------------------------------------ UMMA issuer
     reg_dealloc<72>();
-    if (lane == 0) {
+    {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
       int idx = 0;
-      bool ok = mbar_wait(bar(SB_Q_FULL), 0, ab, p.err, 501);
+      bool ok = mbar_wait_warp(bar(SB_Q_FULL), 0, ab, p.err, 501);
       auto qk = [&](int t) {
         const int st = idx % Cfg::kStages;
-        ok = mbar_wait(bar(SB_FULL + st), (idx / Cfg::kStages) & 1, ab, p.err, 502);
+        ok = mbar_wait_warp(bar(SB_FULL + st), (idx / Cfg::kStages) & 1, ab, p.err, 502);
         if (!ok) return;
         tc_fence_after();
         const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_ss(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+          umma_ss_elect(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
                   idesc_qk, ks > 0);
         }
-        umma_commit(bar(SB_S_FULL + t));
-        umma_commit(bar(SB_EMPTY + st));
+        umma_commit_elect(bar(SB_S_FULL + t));
+        umma_commit_elect(bar(SB_EMPTY + st));
         ++idx;
       };
       auto pv = [&](int t, int j) {
         const int st = idx % Cfg::kStages;
-        ok = mbar_wait(bar(SB_FULL + st), (idx / Cfg::kStages) & 1, ab, p.err, 503);
-        if (ok) ok = mbar_wait(bar(SB_P_FULL + t), j & 1, ab, p.err, 504);
+        ok = mbar_wait_warp(bar(SB_FULL + st), (idx / Cfg::kStages) & 1, ab, p.err, 503);
+        if (ok) ok = mbar_wait_warp(bar(SB_P_FULL + t), j & 1, ab, p.err, 504);
         if (!ok) return;
         tc_fence_after();
         const uint32_t va = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+          umma_ts_elect(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
                   idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(bar(SB_EMPTY + st));
+        umma_commit_elect(bar(SB_EMPTY + st));
         ++idx;
       };
       if (ok && n0 > 0) qk(0);
@@ -246,7 +246,7 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
             pv(t, j);
             if (!ok) break;
             if (j + 1 < nt) qk(t);
-            else umma_commit(bar(SB_O_FULL + t));
+            else umma_commit_elect(bar(SB_O_FULL + t));
           }
         }
       }

@@ -1,0 +1,585 @@
+// Persistent block-sparse gather attention with precomputed (max_q, denom), sm_100a.
+//
+// Work item = one PAIR of neighbouring 64-row query blocks (one 128-row UMMA tile) of one
+// (batch, head) unit, walking the sorted union of the pair's two key-block lists, two listed key
+// blocks (128 keys) per step.  CTAs are persistent and pull items from a global queue; within a
+// head the queue is ordered longest-list-first, heads stay contiguous so that the K/V tiles being
+// gathered by the CTAs in flight fit in L2.
+//
+// Because the probabilities are p = 2^(s*c - (m*c + log2 l)) with m, l given, no row reduction is
+// needed and the two softmax warpgroups split the COLUMNS of a score tile (keys 0-63 / 64-127, i.e.
+// one listed key block each).
+//
+// Tensor memory (512 columns): scores S[2] (2 x 128), probabilities P[2] (2 x 64, packed bf16),
+// output accumulator O (128).  Scores and probabilities have their own double buffers, so the
+// three pipelines only meet through full/empty barriers two steps apart:
+//   Q K^T issuer (warp 9)  : S[s&1] = Q K_s^T           needs K_s and S[s&1] drained by the softmax
+//   softmax (warps 0-7)    : P[s&1] = 2^(S[s&1]*c - t)  needs S[s&1]; P[s&1] consumed by P*V of s-2
+//   P V issuer (warp 11)   : O += P[s&1] V_s            needs both halves of P[s&1] and V_s
+// Warp 8 is the TMA producer of Q and the K ring, warp 12 of the V ring, warp 10 the scheduler (queue +
+// union lists, up to three items ahead).  512 threads; warps 13-15 idle.
+#pragma once
+#include "sm100_ptx.cuh"
+#include "softmax_steps.cuh"
+#include "sparse_attn.cuh"
+
+#ifndef FG_POLY_OF8
+#define FG_POLY_OF8 0
+#endif
+
+namespace fg {
+
+struct SparseMLParams {
+  __nv_bfloat16* o;          // [BH, S, D]
+  const float* max_q;        // [BH, S_pad]
+  const float* denom;        // [BH, S_pad]
+  const int* kb_idx;         // [BH, nqb, list_stride]
+  const int* kb_cnt;         // [BH, nqb]
+  const int* order;          // [BH, npairs] pair indices, longest list first
+  int* queue;                // global item counter (zeroed before the launch)
+  int* err;
+  int S, S_pad, kv_len, nqb, nkb, npairs, n_items, list_stride, list_cap;
+  float scale_log2;
+  long long* stats;          // debug & 8: per-CTA cycle counters [gridDim.x][32]
+  int debug;                 // timing experiments only: 1 = no K/V loads, 2 = no UMMA, 4 = no softmax math
+};
+
+template <int D>
+struct SparseMLCfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kKStages = (D == 128) ? 2 : 4;
+  static constexpr int kVStages = (D == 128) ? 2 : 4;
+  static constexpr int kListBufs = 4;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = 2 * kTileBytes;
+  static constexpr int kOffV = kOffK + kKStages * kTileBytes;
+  static constexpr int kOffBar = kOffV + kVStages * kTileBytes;
+  static constexpr int kBarBytes = 768;
+  static constexpr int kOffList = kOffBar + kBarBytes;   // [kListBufs][list_cap] entries, then [2][words] bitmaps
+  static __host__ __device__ constexpr int smem_bytes(int list_cap, int nkb) {
+    return kOffList + kListBufs * list_cap * 4 + 2 * ((nkb + 31) / 32) * 4 + 1024;
+  }
+};
+
+enum : int {
+  PB_LIST_FULL = 0,    // +list buffer (4)
+  PB_LIST_EMPTY = 4,   // +list buffer (4)
+  PB_Q_FULL = 8,       // +q buffer (2)
+  PB_Q_EMPTY = 10,     // +q buffer (2)
+  PB_K_FULL = 12,      // +stage (<=4)
+  PB_K_EMPTY = 16,     // +stage
+  PB_V_FULL = 20,      // +stage (<=4)
+  PB_V_EMPTY = 24,     // +stage
+  PB_S_FULL = 28,      // +sbuf (2)
+  PB_S_EMPTY = 30,     // +sbuf (2)
+  PB_P_FULL = 32,      // +pbuf*2+half (4)
+  PB_P_EMPTY = 36,     // +pbuf (2)
+  PB_O_FULL = 38,
+  PB_O_EMPTY = 39,
+  PB_COUNT = 40
+};
+
+struct ItemInfo {
+  int n_steps;   // -1: queue exhausted
+  int bh;
+  int pair;
+  int pad;
+};
+
+// 64 score columns -> 32 packed bf16 probability columns, p = 2^(s*c - t_row).
+// kPolyOf8 of every 8 column pairs go through the FMA-pipe polynomial, the rest through MUFU.
+template <int kPolyOf8>
+__device__ __forceinline__ void ml_probs_64(const uint32_t (&r)[64], uint32_t (&pk)[32], int valid, float c,
+                                            float t_row) {
+  const uint64_t c2 = f2_pack(c, c), nt2 = f2_pack(-t_row, -t_row);
+#pragma unroll
+  for (int i = 0; i < 64; i += 2) {
+    float x0, x1, p0, p1;
+    f2_unpack(f2_fma(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, nt2), x0, x1);
+    if (((i >> 1) & 7) < kPolyOf8) {
+      ex2_poly2(x0, x1, p0, p1);
+    } else {
+      p0 = ex2(x0);
+      p1 = ex2(x1);
+    }
+    if (valid < 64) {
+      if (i >= valid) p0 = 0.f;
+      if (i + 1 >= valid) p1 = 0.f;
+    }
+    pk[i >> 1] = pack_bf16(p0, p1);
+  }
+}
+
+// Cycle accounting for tuning builds (-DFG_STATS); compiled out otherwise.
+#ifdef FG_STATS
+#define FG_TW(acc, expr) do { long long t__ = clock64(); expr; acc += clock64() - t__; } while (0)
+#define FG_CLK() clock64()
+#else
+#define FG_TW(acc, expr) do { expr; } while (0)
+#define FG_CLK() 0ll
+#endif
+
+template <int D>
+__global__ void __launch_bounds__(512, 1)
+sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                            const __grid_constant__ CUtensorMap mv, const SparseMLParams p) {
+  using Cfg = SparseMLCfg<D>;
+  constexpr int NLB = Cfg::kListBufs;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bars = sbase + Cfg::kOffBar;
+  auto bar = [&](int i) -> uint32_t { return bars + 8u * uint32_t(i); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::kOffBar + 8 * PB_COUNT);
+  AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * PB_COUNT + 8);
+  volatile ItemInfo* info = reinterpret_cast<volatile ItemInfo*>(smem + Cfg::kOffBar + 8 * PB_COUNT + 16);   // [NLB]
+  uint32_t* lists = reinterpret_cast<uint32_t*>(smem + Cfg::kOffList);                                       // [NLB][cap]
+  uint32_t* bitmaps = lists + NLB * p.list_cap;                                                              // [2][words]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int words = (p.nkb + 31) / 32;
+  constexpr uint32_t kColS = 0, kColP = 256, kColO = 384;
+
+  if (tid == 0) {
+    ab->flag = 0;
+    for (int b = 0; b < NLB; ++b) {
+      mbar_init(bar(PB_LIST_FULL + b), 1);
+      mbar_init(bar(PB_LIST_EMPTY + b), 12);             // two producers + two issuers + 8 softmax warps
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(PB_Q_FULL + b), 1);
+      mbar_init(bar(PB_Q_EMPTY + b), 1);
+      mbar_init(bar(PB_S_FULL + b), 1);
+      mbar_init(bar(PB_S_EMPTY + b), 8);                 // one arrival per softmax warp
+      mbar_init(bar(PB_P_FULL + b * 2 + 0), 4);
+      mbar_init(bar(PB_P_FULL + b * 2 + 1), 4);
+      mbar_init(bar(PB_P_EMPTY + b), 1);
+    }
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(bar(PB_K_FULL + s), 1);
+      mbar_init(bar(PB_K_EMPTY + s), 1);
+      mbar_init(bar(PB_V_FULL + s), 1);
+      mbar_init(bar(PB_V_EMPTY + s), 1);
+    }
+    mbar_init(bar(PB_O_FULL), 1);
+    mbar_init(bar(PB_O_EMPTY), 8);
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 10) {
+    // ------------------------------------------------------------------ scheduler: queue + union lists
+    reg_dealloc<48>();
+    uint32_t* bm0 = bitmaps;
+    uint32_t* bm1 = bitmaps + words;
+    for (int it = 0;; ++it) {
+      const int lb = it % NLB;
+      bool ok = true;
+      if (it >= NLB) ok = mbar_wait(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001);
+      if (!ok) break;
+      int g = 0;
+      if (lane == 0) g = atomicAdd(p.queue, 1);
+      g = __shfl_sync(0xffffffffu, g, 0);
+      if (g >= p.n_items) {
+        if (lane == 0) {
+          info[lb].n_steps = -1;
+          mbar_arrive(bar(PB_LIST_FULL + lb));
+        }
+        break;
+      }
+      const int bh = g / p.npairs;
+      const int pair = p.order[size_t(bh) * p.npairs + (g - bh * p.npairs)];
+      for (int w = lane; w < 2 * words; w += 32) bm0[w] = 0u;
+      __syncwarp();
+      // both halves' counts are fetched before either list is walked
+      int n_half[2];
+      const int* src_half[2];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int qb = pair * 2 + half;
+        n_half[half] = 0;
+        src_half[half] = p.kb_idx;
+        if (qb < p.nqb) {
+          src_half[half] = p.kb_idx + (size_t(bh) * p.nqb + qb) * p.list_stride;
+          n_half[half] = min(p.kb_cnt[size_t(bh) * p.nqb + qb], p.list_stride);
+        }
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t* bm = half ? bm1 : bm0;
+        for (int i = lane; i < n_half[half]; i += 32) {
+          const int kb = src_half[half][i];
+          if (kb >= 0 && kb < p.nkb) atomicOr(&bm[kb >> 5], 1u << (kb & 31));
+        }
+      }
+      __syncwarp();
+      uint32_t* out = lists + lb * p.list_cap;
+      int base = 0;
+      for (int w0 = 0; w0 < words; w0 += 32) {
+        const int w = w0 + lane;
+        const uint32_t a = (w < words) ? bm0[w] : 0u, bb = (w < words) ? bm1[w] : 0u;
+        uint32_t u = a | bb;
+        const int cnt = __popc(u);
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int n = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += n;
+        }
+        int off = base + incl - cnt;
+        while (u) {
+          const int bit = __ffs(u) - 1;
+          u &= u - 1;
+          if (off < p.list_cap)
+            out[off] = uint32_t(w * 32 + bit) | (((a >> bit) & 1u) << 30) | (((bb >> bit) & 1u) << 31);
+          ++off;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (base > p.list_cap - 1) base = p.list_cap - 1;
+      __syncwarp();
+      if (lane == 0) {
+        if (base & 1) {                                  // odd: repeat the last block, kept by nobody
+          out[base] = out[base - 1] & 0x3FFFFFFFu;
+          ++base;
+        }
+        info[lb].bh = bh;
+        info[lb].pair = pair;
+        info[lb].n_steps = base >> 1;
+        mbar_arrive(bar(PB_LIST_FULL + lb));
+      }
+      __syncwarp();
+    }
+  } else if (warp == 8 || warp == 12) {
+    // ------------------------------------------------------------------ TMA producers
+    // Warp 8 feeds Q (per item) and the K ring, warp 12 the V ring.  They walk the same item / step
+    // sequence independently, so a V stage that is still waiting for its P*V product never holds
+    // back the K tiles of the steps ahead.
+    reg_dealloc<48>();
+    if (lane == 0) {
+      const bool is_k = (warp == 8);
+      const CUtensorMap* m = is_k ? &mk : &mv;
+      if (is_k) tma_prefetch_desc(&mq);
+      tma_prefetch_desc(m);
+      const int n_stages = is_k ? Cfg::kKStages : Cfg::kVStages;
+      const uint32_t ring = sbase + (is_k ? Cfg::kOffK : Cfg::kOffV);
+      const int full0 = is_k ? PB_K_FULL : PB_V_FULL, empty0 = is_k ? PB_K_EMPTY : PB_V_EMPTY;
+      int s = 0, u = 0;
+      bool ok = true;
+      for (int it = 0; ok; ++it) {
+        const int lb = it % NLB;
+        ok = mbar_wait(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1102);
+        if (!ok) break;
+        const int n = info[lb].n_steps;
+        if (n < 0) break;
+        if (n > 0) {
+          const int bh = info[lb].bh, pair = info[lb].pair;
+          if (is_k) {
+            const int qb = u & 1;
+            if (u >= 2) ok = mbar_wait(bar(PB_Q_EMPTY + qb), ((u >> 1) - 1) & 1, ab, p.err, 1103);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar(PB_Q_FULL + qb), Cfg::kTileBytes);
+            for (int h = 0; h < Cfg::kHalves; ++h)
+              tma_load_3d(sbase + Cfg::kOffQ + qb * Cfg::kTileBytes + h * 16384, &mq, bar(PB_Q_FULL + qb), h * 64,
+                          pair * 128, bh);
+          }
+          const uint32_t* list = lists + lb * p.list_cap;
+          for (int j = 0; j < n && ok; ++j, ++s) {
+            const int kb0 = entry_kb(list[2 * j]), kb1 = entry_kb(list[2 * j + 1]);
+            const int st = s % n_stages, f = s / n_stages;
+            if (f > 0) ok = mbar_wait(bar(empty0 + st), (f - 1) & 1, ab, p.err, 1104);
+            if (!ok) break;
+            const uint32_t dst = ring + st * Cfg::kTileBytes, full_bar = bar(full0 + st);
+            if (p.debug & 1) {
+              mbar_arrive(full_bar);
+            } else {
+              mbar_arrive_expect_tx(full_bar, Cfg::kTileBytes);
+              for (int h = 0; h < Cfg::kHalves; ++h) {
+                tma_load_3d(dst + h * 16384, m, full_bar, h * 64, kb0 * 64, bh);
+                tma_load_3d(dst + h * 16384 + 8192, m, full_bar, h * 64, kb1 * 64, bh);
+              }
+            }
+          }
+          ++u;
+        }
+        if (ok) mbar_arrive(bar(PB_LIST_EMPTY + lb));
+      }
+      if (!ok) {
+        for (int i = max(0, s - n_stages); i < s; ++i) mbar_wait_brief(bar(full0 + i % n_stages), (i / n_stages) & 1);
+        if (is_k)
+          for (int i = max(0, u - 2); i < u; ++i) mbar_wait_brief(bar(PB_Q_FULL + (i & 1)), (i >> 1) & 1);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ Q K^T issuer
+    // Whole warp, uniform control flow; each instruction is issued by one elected lane.
+    reg_dealloc<48>();
+    const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
+    int s = 0, u = 0;
+    bool ok = true;
+    long long w_k = 0, w_se = 0, w_misc = 0, t_start = FG_CLK();
+    for (int it = 0; ok; ++it) {
+      const int lb = it % NLB;
+      FG_TW(w_misc, ok = mbar_wait_warp(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1201));
+      if (!ok) break;
+      const int n = info[lb].n_steps;
+      if (n < 0) break;
+      if (lane == 0) mbar_arrive(bar(PB_LIST_EMPTY + lb));        // only n is needed from the list buffer
+      __syncwarp();
+      if (n > 0) {
+        const int qb = u & 1;
+        FG_TW(w_misc, ok = mbar_wait_warp(bar(PB_Q_FULL + qb), (u >> 1) & 1, ab, p.err, 1202));
+        const uint32_t qa = sbase + Cfg::kOffQ + qb * Cfg::kTileBytes;
+        for (int j = 0; j < n && ok; ++j, ++s) {
+          const int ks = s % Cfg::kKStages, sbuf = s & 1;
+          FG_TW(w_k, ok = mbar_wait_warp(bar(PB_K_FULL + ks), (s / Cfg::kKStages) & 1, ab, p.err, 1203));
+          if (ok && s >= 2) FG_TW(w_se, ok = mbar_wait_warp(bar(PB_S_EMPTY + sbuf), ((s >> 1) - 1) & 1, ab, p.err, 1204));
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t ka = sbase + Cfg::kOffK + ks * Cfg::kTileBytes;
+          if (!(p.debug & 2)) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+              umma_ss_elect(tmem + kColS + sbuf * 128, umma_smem_desc_sw128(qa + off, 16, 1024),
+                            umma_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0);
+            }
+          }
+          umma_commit_elect(bar(PB_S_FULL + sbuf));
+          umma_commit_elect(bar(PB_K_EMPTY + ks));
+          if (j == n - 1) umma_commit_elect(bar(PB_Q_EMPTY + qb));
+        }
+        ++u;
+      }
+    }
+    if (p.stats && lane == 0) {
+      long long* st_ = p.stats + size_t(blockIdx.x) * 32;
+      st_[0] = FG_CLK() - t_start; st_[1] = w_k; st_[2] = w_se; st_[3] = w_misc; st_[4] = s;
+    }
+  } else if (warp == 11) {
+    // ------------------------------------------------------------------ P V issuer
+    reg_dealloc<48>();
+    const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
+    int s = 0, u = 0;
+    bool ok = true;
+    long long w_v = 0, w_p = 0, w_o = 0, w_misc = 0, t_start = FG_CLK();
+    for (int it = 0; ok; ++it) {
+      const int lb = it % NLB;
+      FG_TW(w_misc, ok = mbar_wait_warp(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1301));
+      if (!ok) break;
+      const int n = info[lb].n_steps;
+      if (n < 0) break;
+      if (lane == 0) mbar_arrive(bar(PB_LIST_EMPTY + lb));        // only n is needed from the list buffer
+      __syncwarp();
+      if (n > 0) {
+        // the accumulator is single-buffered: the previous item's rows must have been read out
+        if (u >= 1) FG_TW(w_o, ok = mbar_wait_warp(bar(PB_O_EMPTY), (u - 1) & 1, ab, p.err, 1302));
+        for (int j = 0; j < n && ok; ++j, ++s) {
+          const int vs = s % Cfg::kVStages, pbuf = s & 1;
+          FG_TW(w_v, ok = mbar_wait_warp(bar(PB_V_FULL + vs), (s / Cfg::kVStages) & 1, ab, p.err, 1303));
+          const uint32_t va = sbase + Cfg::kOffV + vs * Cfg::kTileBytes;
+          for (int hf = 0; hf < 2 && ok; ++hf) {
+            FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + pbuf * 2 + hf), (s >> 1) & 1, ab, p.err, 1304));
+            if (!ok) break;
+            tc_fence_after();
+            if (!(p.debug & 2)) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                const int ks = hf * 4 + kk;
+                umma_ts_elect(tmem + kColO, tmem + kColP + pbuf * 64 + ks * 8,
+                              umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+              }
+            }
+          }
+          if (!ok) break;
+          umma_commit_elect(bar(PB_V_EMPTY + vs));
+          umma_commit_elect(bar(PB_P_EMPTY + pbuf));
+          if (j == n - 1) umma_commit_elect(bar(PB_O_FULL));
+        }
+        ++u;
+      }
+    }
+    if (p.stats && lane == 0) {
+      long long* st_ = p.stats + size_t(blockIdx.x) * 32 + 8;
+      st_[0] = FG_CLK() - t_start; st_[1] = w_v; st_[2] = w_p; st_[3] = w_o; st_[4] = w_misc;
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ softmax warpgroups
+    // Both warpgroups work on every step: warpgroup g turns the 64 columns of listed key block g of
+    // the step (keys g*64 .. g*64+63) into probabilities, one query row per thread.
+    reg_alloc<208>();
+    const int wg = warp >> 2, wq = warp & 3, half = wq >> 1;
+    const int row_in_tile = wq * 32 + lane;
+    const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
+    const float c = p.scale_log2;
+    constexpr int kOCols = D / 2;                        // output columns stored by this warpgroup
+    int s = 0, u = 0;
+    bool ok = true;
+    long long w_s = 0, w_list = 0, w_epi = 0, w_pe = 0, t_math = 0, t_prol = 0, t_epiw = 0, t_ld = 0, t_st = 0,
+              t_start = FG_CLK();
+    bool pe = false;                                     // pending epilogue of the previous item
+    int pe_par = 0;
+    __nv_bfloat16* pe_orow = nullptr;
+    bool pe_in = false;
+    auto epilogue = [&]() {
+      FG_TW(w_epi, ok = mbar_wait(bar(PB_O_FULL), pe_par, ab, p.err, 1401));
+      if (!ok) return;
+      long long te0 = FG_CLK();
+      tc_fence_after();
+      uint32_t o[kOCols];
+#pragma unroll
+      for (int cc = 0; cc < kOCols / 32; ++cc)
+        tmem_ld32(lane_base + kColO + wg * kOCols + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[cc * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(PB_O_EMPTY));
+      if (pe_in) {
+#pragma unroll
+        for (int i = 0; i < kOCols / 8; ++i) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
+          v.y = pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
+          v.z = pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
+          v.w = pack_bf16(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7]));
+          *reinterpret_cast<uint4*>(pe_orow + wg * kOCols + i * 8) = v;
+        }
+      }
+      pe = false;
+      t_epiw += FG_CLK() - te0;
+    };
+    for (int it = 0; ok; ++it) {
+      const int lb = it % NLB;
+      FG_TW(w_list, ok = mbar_wait(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1402));
+      if (!ok) break;
+      const int n = info[lb].n_steps;
+      if (n < 0) break;
+      const int bh = info[lb].bh, pair = info[lb].pair;
+      const int row = pair * 128 + row_in_tile;
+      __nv_bfloat16* orow = p.o + (size_t(bh) * p.S + row) * D;
+      if (n == 0) {
+        if (row < p.S) {
+#pragma unroll
+          for (int i = 0; i < kOCols / 8; ++i) reinterpret_cast<uint4*>(orow + wg * kOCols)[i] = make_uint4(0, 0, 0, 0);
+        }
+      } else {
+        float t_row = INFINITY;
+        long long tp0 = FG_CLK();
+        if (row < p.S) {
+          const size_t off = size_t(bh) * p.S_pad + row;
+          t_row = p.max_q[off] * c + log2f(p.denom[off]);
+        }
+#ifdef FG_STATS
+        if (t_row == 12345.678f) t_prol += 1;            // keeps the loads inside the timed span
+#endif
+        t_prol += FG_CLK() - tp0;
+        const uint32_t* list = lists + lb * p.list_cap;
+        for (int j = 0; j < n; ++j, ++s) {
+          const uint32_t e = list[2 * j + wg];
+          const int valid = ((e >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e) * 64) : 0;
+          const int sbuf = s & 1;
+          FG_TW(w_s, ok = mbar_wait(bar(PB_S_FULL + sbuf), (s >> 1) & 1, ab, p.err, 1403));
+          if (!ok) break;
+          tc_fence_after();
+          long long tm0 = FG_CLK();
+          uint32_t pk[32];
+          if (valid > 0 && !(p.debug & 4)) {             // warp-uniform
+            uint32_t r[64];
+            const uint32_t a = lane_base + kColS + sbuf * 128 + wg * 64;
+            tmem_ld32(a, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tmem_ld32(a + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tmem_ld_wait();
+            t_ld += FG_CLK() - tm0;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(PB_S_EMPTY + sbuf));   // scores are in registers: buffer reusable
+            ml_probs_64<FG_POLY_OF8>(r, pk, valid, c, t_row);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(PB_S_EMPTY + sbuf));
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pk[i] = 0u;
+          }
+          t_math += FG_CLK() - tm0;
+          // P[s&1] was last read by the P*V product of step s-2
+          if (s >= 2) FG_TW(w_pe, ok = mbar_wait(bar(PB_P_EMPTY + sbuf), ((s >> 1) - 1) & 1, ab, p.err, 1404));
+          if (!ok) break;
+          tc_fence_after();
+          long long ts0 = FG_CLK();
+          tmem_st32(lane_base + kColP + sbuf * 64 + wg * 32, pk);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(PB_P_FULL + sbuf * 2 + wg));
+          t_st += FG_CLK() - ts0;
+          if (j == 0 && pe) {
+            epilogue();
+            if (!ok) break;
+          }
+        }
+        if (!ok) break;
+        if (pe) epilogue();                              // (only when the loop above did not run it)
+        if (!ok) break;
+        pe = true;
+        pe_par = u & 1;
+        pe_orow = orow;
+        pe_in = row < p.S;
+        ++u;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(PB_LIST_EMPTY + lb));
+    }
+    if (ok && pe) epilogue();
+    if (p.stats && (warp & 3) == 0 && lane == 0) {
+      long long* st_ = p.stats + size_t(blockIdx.x) * 32 + 16 + 8 * wg;
+      st_[0] = FG_CLK() - t_start; st_[1] = w_s; st_[2] = w_list; st_[3] = w_epi; st_[4] = t_math;
+      st_[5] = w_pe; st_[6] = t_prol; st_[7] = t_epiw;
+      if (wg == 1) { st_[2] = t_ld; st_[3] = t_st; }
+    }
+  } else {
+    reg_dealloc<48>();                                   // warps 13-15: idle
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// Per head: order the query-block pairs by list length, longest first (rank by counting).
+// grid (BH), 256 threads, dynamic shared memory npairs ints.  Block 0 also clears the queue counter.
+__global__ void __launch_bounds__(256)
+sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int* __restrict__ queue, int nqb,
+                    int npairs) {
+  extern __shared__ int len[];
+  const int bh = blockIdx.x;
+  if (bh == 0 && threadIdx.x == 0) *queue = 0;
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int a = kb_cnt[size_t(bh) * nqb + 2 * i];
+    const int b = (2 * i + 1 < nqb) ? kb_cnt[size_t(bh) * nqb + 2 * i + 1] : 0;
+    len[i] = a + b;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int li = len[i];
+    int rank = 0;
+    for (int j = 0; j < npairs; ++j) {
+      const int lj = len[j];
+      rank += (lj > li || (lj == li && j < i)) ? 1 : 0;
+    }
+    order[size_t(bh) * npairs + rank] = i;
+  }
+}
+
+}  // namespace fg

@@ -116,10 +116,18 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
 /* Block-sparse attention with the precomputed (max_q, denom) of the softmax over ALL keys: rows
  * of query block qb attend to the listed key blocks only, probabilities are not renormalised
  * (the masked attention of python/test_mask.py:37-54).  The gather of K/V tiles by index replaces
- * include/sparseattn_asyncgatherload_padded.cuh:130-256 and include/asyncloadutils.cuh:73-153. */
+ * include/sparseattn_asyncgatherload_padded.cuh:130-256 and include/asyncloadutils.cuh:73-153.
+ * `workspace` (device memory, >= fgattn_sp_attn_workspace_bytes, 16-byte aligned) holds the work queue
+ * of the persistent kernel. */
 int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                              const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
-                             int heads, int seq, int D, int kv_seq_len, float scale, void* stream);
+                             int heads, int seq, int D, int kv_seq_len, float scale, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs (work-queue counter + per-head processing
+ * order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
+ * two calls that may overlap on the device must not share it. */
+size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);
 
 /* Same gather kernel with the renormalising softmax of the sp_attn operator (softmax over the kept
  * keys only, include/sparseattn_asyncgatherload_padded.cuh:198-249) on key-block lists. */

@@ -49,7 +49,7 @@ def test_argument_validation_needs_no_device():
     assert lib.fgattn_full_attn(buf, ctypes.c_void_p(0x1008), buf, buf, 1, 1, 64, 64, 64, 0.0, null) == 3
     assert lib.fgattn_maxq_denom(null, null, buf, buf, 1, 1, 64, 64, 64, 0.0, null) == 1
     assert lib.fgattn_booleanmask_to_indexmask(buf, buf, buf, 1, 1, 64, 0, 128, null) == 1
-    assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 0.0, null) == 1
+    assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 0.0, buf, 64, null) == 1
 
 
 def test_python_layer_refuses_cpu_tensors():
