@@ -419,14 +419,14 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
     auto kern = fg::sparse_ml_persistent_kernel<128>;
     r = set_smem(kern, smem);
     if (r) return r;
-    kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
+    kern<<<grid, fg::SparseMLCfg<128>::kThreads, smem, st>>>(mq, mk, mv, p);
   } else {
     const int smem = fg::SparseMLCfg<64>::smem_bytes(p.list_cap, p.nkb);
     if (smem > 232448) return FGATTN_UNSUPPORTED;
     auto kern = fg::sparse_ml_persistent_kernel<64>;
     r = set_smem(kern, smem);
     if (r) return r;
-    kern<<<grid, 512, smem, st>>>(mq, mk, mv, p);
+    kern<<<grid, fg::SparseMLCfg<64>::kThreads, smem, st>>>(mq, mk, mv, p);
   }
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;

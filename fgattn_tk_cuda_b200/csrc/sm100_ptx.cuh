@@ -121,6 +121,14 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ab
   return __all_sync(0xffffffffu, ok);
 }
 
+// Converged-warp wait where only lane 0 polls the barrier; the other lanes park at the shuffle.
+// Keeps the number of threads hammering shared memory with try_wait small.
+__device__ __forceinline__ bool mbar_wait_leader(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ab, err, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // Wait used only on the abort path: short budget, no error recording.
 __device__ __forceinline__ void mbar_wait_brief(uint32_t bar, uint32_t parity) {
   long long t0 = clock64();

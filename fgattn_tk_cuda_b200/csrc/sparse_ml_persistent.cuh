@@ -13,11 +13,11 @@
 // Tensor memory (512 columns): scores S[2] (2 x 128), probabilities P[2] (2 x 64, packed bf16),
 // output accumulator O (128).  Scores and probabilities have their own double buffers, so the
 // three pipelines only meet through full/empty barriers two steps apart:
-//   Q K^T issuer (warp 9)  : S[s&1] = Q K_s^T           needs K_s and S[s&1] drained by the softmax
-//   softmax (warps 0-7)    : P[s&1] = 2^(S[s&1]*c - t)  needs S[s&1]; P[s&1] consumed by P*V of s-2
-//   P V issuer (warp 11)   : O += P[s&1] V_s            needs both halves of P[s&1] and V_s
-// Warp 8 is the TMA producer of Q and the K ring, warp 12 of the V ring, warp 10 the scheduler (queue +
-// union lists, up to three items ahead).  512 threads; warps 13-15 idle.
+//   Q K^T issuer           : S[s&1] = Q K_s^T           needs K_s and S[s&1] drained by the softmax
+//   softmax warpgroups     : P[s&1] = 2^(S[s&1]*c - t)  needs S[s&1]; P[s&1] consumed by P*V of s-2
+//   P V issuer             : O += P[s&1] V_s            needs both halves of P[s&1] and V_s
+// Service warps after the softmax warps: TMA producer of Q and the K ring, Q K^T issuer, scheduler
+// (queue + union lists, up to three items ahead), P V issuer, TMA producer of the V ring.
 #pragma once
 #include "sm100_ptx.cuh"
 #include "softmax_steps.cuh"
@@ -25,6 +25,9 @@
 
 #ifndef FG_POLY_OF8
 #define FG_POLY_OF8 0
+#endif
+#ifndef FG_ML_SMWGS
+#define FG_ML_SMWGS 4          // softmax warpgroups per CTA (2 or 4)
 #endif
 
 namespace fg {
@@ -51,6 +54,16 @@ struct SparseMLCfg {
   static constexpr int kKStages = (D == 128) ? 2 : 4;
   static constexpr int kVStages = (D == 128) ? 2 : 4;
   static constexpr int kListBufs = 4;
+  // warp roles: [0, kSmWarps) softmax, then K producer, QK issuer, scheduler, PV issuer, V producer
+  static constexpr int kSmWGs = FG_ML_SMWGS;
+  static constexpr int kSmWarps = 4 * kSmWGs;
+  static constexpr int kWarpProdK = kSmWarps, kWarpQK = kSmWarps + 1, kWarpSched = kSmWarps + 2,
+                       kWarpPV = kSmWarps + 3, kWarpProdV = kSmWarps + 4;
+  static constexpr int kThreads = 32 * (kSmWarps + 8);
+  static constexpr int kColsPerWG = 128 / kSmWGs;         // score columns per softmax warpgroup and step
+  // registers: the CTA owns (launch registers x threads); service warps shrink, softmax warps grow
+  static constexpr int kRegsService = (kSmWGs == 2) ? 48 : 40;
+  static constexpr int kRegsSoftmax = (kSmWGs == 2) ? 208 : 96;
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = 2 * kTileBytes;
   static constexpr int kOffV = kOffK + kKStages * kTileBytes;
@@ -73,11 +86,11 @@ enum : int {
   PB_V_EMPTY = 24,     // +stage
   PB_S_FULL = 28,      // +sbuf (2)
   PB_S_EMPTY = 30,     // +sbuf (2)
-  PB_P_FULL = 32,      // +pbuf*2+half (4)
-  PB_P_EMPTY = 36,     // +pbuf (2)
-  PB_O_FULL = 38,
-  PB_O_EMPTY = 39,
-  PB_COUNT = 40
+  PB_P_EMPTY = 32,     // +pbuf (2)
+  PB_O_FULL = 34,
+  PB_O_EMPTY = 35,
+  PB_P_FULL = 36,      // +pbuf*kSmWGs + warpgroup (<= 8)
+  PB_COUNT = 44
 };
 
 struct ItemInfo {
@@ -87,23 +100,27 @@ struct ItemInfo {
   int pad;
 };
 
-// 64 score columns -> 32 packed bf16 probability columns, p = 2^(s*c - t_row).
+// N score columns -> N/2 packed bf16 probability columns, p = 2^(s*c - t_row).
 // kPolyOf8 of every 8 column pairs go through the FMA-pipe polynomial, the rest through MUFU.
-template <int kPolyOf8>
-__device__ __forceinline__ void ml_probs_64(const uint32_t (&r)[64], uint32_t (&pk)[32], int valid, float c,
-                                            float t_row) {
+template <int kPolyOf8, int N>
+__device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[N / 2], int valid, float c,
+                                         float t_row) {
   const uint64_t c2 = f2_pack(c, c), nt2 = f2_pack(-t_row, -t_row);
 #pragma unroll
-  for (int i = 0; i < 64; i += 2) {
+  for (int i = 0; i < N; i += 2) {
     float x0, x1, p0, p1;
     f2_unpack(f2_fma(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, nt2), x0, x1);
+#ifdef FG_NO_EX2
+    p0 = x0; p1 = x1;
+#else
     if (((i >> 1) & 7) < kPolyOf8) {
       ex2_poly2(x0, x1, p0, p1);
     } else {
       p0 = ex2(x0);
       p1 = ex2(x1);
     }
-    if (valid < 64) {
+#endif
+    if (valid < N) {
       if (i >= valid) p0 = 0.f;
       if (i + 1 >= valid) p1 = 0.f;
     }
@@ -121,7 +138,7 @@ __device__ __forceinline__ void ml_probs_64(const uint32_t (&r)[64], uint32_t (&
 #endif
 
 template <int D>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(SparseMLCfg<D>::kThreads, 1)
 sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                             const __grid_constant__ CUtensorMap mv, const SparseMLParams p) {
   using Cfg = SparseMLCfg<D>;
@@ -145,15 +162,14 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     ab->flag = 0;
     for (int b = 0; b < NLB; ++b) {
       mbar_init(bar(PB_LIST_FULL + b), 1);
-      mbar_init(bar(PB_LIST_EMPTY + b), 12);             // two producers + two issuers + 8 softmax warps
+      mbar_init(bar(PB_LIST_EMPTY + b), 4 + Cfg::kSmWarps);   // two producers + two issuers + softmax warps
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(PB_Q_FULL + b), 1);
       mbar_init(bar(PB_Q_EMPTY + b), 1);
       mbar_init(bar(PB_S_FULL + b), 1);
-      mbar_init(bar(PB_S_EMPTY + b), 8);                 // one arrival per softmax warp
-      mbar_init(bar(PB_P_FULL + b * 2 + 0), 4);
-      mbar_init(bar(PB_P_FULL + b * 2 + 1), 4);
+      mbar_init(bar(PB_S_EMPTY + b), Cfg::kSmWarps);     // one arrival per softmax warp
+      for (int g = 0; g < Cfg::kSmWGs; ++g) mbar_init(bar(PB_P_FULL + b * Cfg::kSmWGs + g), 4);
       mbar_init(bar(PB_P_EMPTY + b), 1);
     }
     for (int s = 0; s < 4; ++s) {
@@ -163,10 +179,10 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       mbar_init(bar(PB_V_EMPTY + s), 1);
     }
     mbar_init(bar(PB_O_FULL), 1);
-    mbar_init(bar(PB_O_EMPTY), 8);
+    mbar_init(bar(PB_O_EMPTY), Cfg::kSmWarps);
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == Cfg::kWarpProdK) {
     __syncwarp();
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
@@ -176,9 +192,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 10) {
+  if (warp == Cfg::kWarpSched) {
     // ------------------------------------------------------------------ scheduler: queue + union lists
-    reg_dealloc<48>();
+    reg_dealloc<Cfg::kRegsService>();
     uint32_t* bm0 = bitmaps;
     uint32_t* bm1 = bitmaps + words;
     for (int it = 0;; ++it) {
@@ -259,14 +275,14 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       }
       __syncwarp();
     }
-  } else if (warp == 8 || warp == 12) {
+  } else if (warp == Cfg::kWarpProdK || warp == Cfg::kWarpProdV) {
     // ------------------------------------------------------------------ TMA producers
     // Warp 8 feeds Q (per item) and the K ring, warp 12 the V ring.  They walk the same item / step
     // sequence independently, so a V stage that is still waiting for its P*V product never holds
     // back the K tiles of the steps ahead.
-    reg_dealloc<48>();
+    reg_dealloc<Cfg::kRegsService>();
     if (lane == 0) {
-      const bool is_k = (warp == 8);
+      const bool is_k = (warp == Cfg::kWarpProdK);
       const CUtensorMap* m = is_k ? &mk : &mv;
       if (is_k) tma_prefetch_desc(&mq);
       tma_prefetch_desc(m);
@@ -319,10 +335,10 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           for (int i = max(0, u - 2); i < u; ++i) mbar_wait_brief(bar(PB_Q_FULL + (i & 1)), (i >> 1) & 1);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::kWarpQK) {
     // ------------------------------------------------------------------ Q K^T issuer
     // Whole warp, uniform control flow; each instruction is issued by one elected lane.
-    reg_dealloc<48>();
+    reg_dealloc<Cfg::kRegsService>();
     const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
     int s = 0, u = 0;
     bool ok = true;
@@ -365,9 +381,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       long long* st_ = p.stats + size_t(blockIdx.x) * 32;
       st_[0] = FG_CLK() - t_start; st_[1] = w_k; st_[2] = w_se; st_[3] = w_misc; st_[4] = s;
     }
-  } else if (warp == 11) {
+  } else if (warp == Cfg::kWarpPV) {
     // ------------------------------------------------------------------ P V issuer
-    reg_dealloc<48>();
+    reg_dealloc<Cfg::kRegsService>();
     const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
     int s = 0, u = 0;
     bool ok = true;
@@ -387,14 +403,15 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           const int vs = s % Cfg::kVStages, pbuf = s & 1;
           FG_TW(w_v, ok = mbar_wait_warp(bar(PB_V_FULL + vs), (s / Cfg::kVStages) & 1, ab, p.err, 1303));
           const uint32_t va = sbase + Cfg::kOffV + vs * Cfg::kTileBytes;
-          for (int hf = 0; hf < 2 && ok; ++hf) {
-            FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + pbuf * 2 + hf), (s >> 1) & 1, ab, p.err, 1304));
+          constexpr int kStepsPerWG = Cfg::kColsPerWG / 16;     // UMMA k-steps (16 keys) per softmax warpgroup
+          for (int g = 0; g < Cfg::kSmWGs && ok; ++g) {
+            FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + pbuf * Cfg::kSmWGs + g), (s >> 1) & 1, ab, p.err, 1304));
             if (!ok) break;
             tc_fence_after();
             if (!(p.debug & 2)) {
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                const int ks = hf * 4 + kk;
+              for (int kk = 0; kk < kStepsPerWG; ++kk) {
+                const int ks = g * kStepsPerWG + kk;
                 umma_ts_elect(tmem + kColO, tmem + kColP + pbuf * 64 + ks * 8,
                               umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
               }
@@ -412,16 +429,21 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       long long* st_ = p.stats + size_t(blockIdx.x) * 32 + 8;
       st_[0] = FG_CLK() - t_start; st_[1] = w_v; st_[2] = w_p; st_[3] = w_o; st_[4] = w_misc;
     }
-  } else if (warp < 8) {
+  } else if (warp < Cfg::kSmWarps) {
     // ------------------------------------------------------------------ softmax warpgroups
-    // Both warpgroups work on every step: warpgroup g turns the 64 columns of listed key block g of
-    // the step (keys g*64 .. g*64+63) into probabilities, one query row per thread.
-    reg_alloc<208>();
+    // Every softmax warpgroup works on every step: warpgroup g turns kColsPerWG columns of the
+    // 128-key score tile (keys g*kColsPerWG ...) into probabilities, one query row per thread.  More
+    // warpgroups = narrower slices per warp and more warps per sub-partition to hide the
+    // wait / load / store / signal latencies of a step behind other warps' exponentials.
+    reg_alloc<Cfg::kRegsSoftmax>();
     const int wg = warp >> 2, wq = warp & 3, half = wq >> 1;
     const int row_in_tile = wq * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
     const float c = p.scale_log2;
-    constexpr int kOCols = D / 2;                        // output columns stored by this warpgroup
+    constexpr int kOCols = D / Cfg::kSmWGs;              // output columns stored by this warpgroup
+    constexpr int kCols = Cfg::kColsPerWG;
+    const int kb_sel = wg / (Cfg::kSmWGs / 2);           // which of the step's two key blocks
+    const int col_in_kb = (wg % (Cfg::kSmWGs / 2)) * kCols;
     int s = 0, u = 0;
     bool ok = true;
     long long w_s = 0, w_list = 0, w_epi = 0, w_pe = 0, t_math = 0, t_prol = 0, t_epiw = 0, t_ld = 0, t_st = 0,
@@ -436,9 +458,13 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       long long te0 = FG_CLK();
       tc_fence_after();
       uint32_t o[kOCols];
+      if constexpr (kOCols >= 32) {
 #pragma unroll
-      for (int cc = 0; cc < kOCols / 32; ++cc)
-        tmem_ld32(lane_base + kColO + wg * kOCols + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[cc * 32]));
+        for (int cc = 0; cc < kOCols / 32; ++cc)
+          tmem_ld32(lane_base + kColO + wg * kOCols + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[cc * 32]));
+      } else {
+        tmem_ld16(lane_base + kColO + wg * kOCols, *reinterpret_cast<uint32_t(*)[16]>(&o[0]));
+      }
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
@@ -484,31 +510,33 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         t_prol += FG_CLK() - tp0;
         const uint32_t* list = lists + lb * p.list_cap;
         for (int j = 0; j < n; ++j, ++s) {
-          const uint32_t e = list[2 * j + wg];
-          const int valid = ((e >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e) * 64) : 0;
+          const uint32_t e = list[2 * j + kb_sel];
+          const int valid_kb = ((e >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e) * 64) : 0;
+          const int valid = max(0, min(kCols, valid_kb - col_in_kb));
           const int sbuf = s & 1;
           FG_TW(w_s, ok = mbar_wait(bar(PB_S_FULL + sbuf), (s >> 1) & 1, ab, p.err, 1403));
           if (!ok) break;
           tc_fence_after();
           long long tm0 = FG_CLK();
-          uint32_t pk[32];
+          uint32_t pk[kCols / 2];
           if (valid > 0 && !(p.debug & 4)) {             // warp-uniform
-            uint32_t r[64];
-            const uint32_t a = lane_base + kColS + sbuf * 128 + wg * 64;
-            tmem_ld32(a, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-            tmem_ld32(a + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            uint32_t r[kCols];
+            const uint32_t a = lane_base + kColS + sbuf * 128 + wg * kCols;
+#pragma unroll
+            for (int cc = 0; cc < kCols / 32; ++cc)
+              tmem_ld32(a + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
             tmem_ld_wait();
             t_ld += FG_CLK() - tm0;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(PB_S_EMPTY + sbuf));   // scores are in registers: buffer reusable
-            ml_probs_64<FG_POLY_OF8>(r, pk, valid, c, t_row);
+            ml_probs<FG_POLY_OF8, kCols>(r, pk, valid, c, t_row);
           } else {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(PB_S_EMPTY + sbuf));
 #pragma unroll
-            for (int i = 0; i < 32; ++i) pk[i] = 0u;
+            for (int i = 0; i < kCols / 2; ++i) pk[i] = 0u;
           }
           t_math += FG_CLK() - tm0;
           // P[s&1] was last read by the P*V product of step s-2
@@ -516,11 +544,12 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           if (!ok) break;
           tc_fence_after();
           long long ts0 = FG_CLK();
-          tmem_st32(lane_base + kColP + sbuf * 64 + wg * 32, pk);
+          if constexpr (kCols == 64) tmem_st32(lane_base + kColP + sbuf * 64 + wg * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+          else tmem_st16(lane_base + kColP + sbuf * 64 + wg * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(PB_P_FULL + sbuf * 2 + wg));
+          if (lane == 0) mbar_arrive(bar(PB_P_FULL + sbuf * Cfg::kSmWGs + wg));
           t_st += FG_CLK() - ts0;
           if (j == 0 && pe) {
             epilogue();
@@ -540,18 +569,18 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       if (lane == 0) mbar_arrive(bar(PB_LIST_EMPTY + lb));
     }
     if (ok && pe) epilogue();
-    if (p.stats && (warp & 3) == 0 && lane == 0) {
+    if (p.stats && wg < 2 && (warp & 3) == 0 && lane == 0) {
       long long* st_ = p.stats + size_t(blockIdx.x) * 32 + 16 + 8 * wg;
       st_[0] = FG_CLK() - t_start; st_[1] = w_s; st_[2] = w_list; st_[3] = w_epi; st_[4] = t_math;
       st_[5] = w_pe; st_[6] = t_prol; st_[7] = t_epiw;
       if (wg == 1) { st_[2] = t_ld; st_[3] = t_st; }
     }
   } else {
-    reg_dealloc<48>();                                   // warps 13-15: idle
+    reg_dealloc<Cfg::kRegsService>();                    // padding warps: idle
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == Cfg::kWarpProdK) {
     __syncwarp();
     tmem_dealloc(tmem, 512);
   }
