@@ -36,6 +36,8 @@ PROTOTYPES = {
     "fgattn_block_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f, _vp,
                                       _sz, _vp]),
+    "fgattn_block_index_lists_noalloc": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f,
+                                              _vp]),
     "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
@@ -166,6 +168,21 @@ def block_index_lists(kb_indices, kb_counts, max_q, denom, q, k, threshold, scra
         _call("fgattn_block_index_lists", _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3], _ptr(max_q),
               _ptr(denom), _ptr(o), _ptr(q), _ptr(k), _ptr(v), float(threshold), B, H, S, D, kv_seq_len or S, scale,
               _ptr(scratch), scratch.numel() * scratch.element_size(), _stream(q))
+
+
+NOALLOC_SCRATCH_BYTES = 64 << 20
+
+
+def block_index_lists_noalloc(kb_indices, kb_counts, max_q, denom, q, k, threshold, o=None, v=None, kv_seq_len=None,
+                              scale=0.0):
+    """fgattn_block_index_lists_noalloc: same results as block_index_lists, scratch built into the
+    library (no allocation anywhere on this path; one (batch, head) unit must fit in 64 MiB)."""
+    _check_qkv(q, k, o, v)
+    B, H, S, D = q.shape
+    with torch.cuda.device(q.device):
+        _call("fgattn_block_index_lists_noalloc", _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3], _ptr(max_q),
+              _ptr(denom), _ptr(o), _ptr(q), _ptr(k), _ptr(v), float(threshold), B, H, S, D, kv_seq_len or S, scale,
+              _stream(q))
 
 
 def sp_attn_workspace_bytes(B, H, S) -> int:

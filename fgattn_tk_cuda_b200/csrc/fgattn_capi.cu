@@ -359,6 +359,94 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
   return FGATTN_OK;
 }
 
+// ---- allocation-free variant of fgattn_block_index_lists --------------------------------------
+// Scratch and error word live in the library image.  In host code the names below are host-side
+// stand-ins, not device addresses: the device addresses are looked up once per device with
+// cudaGetSymbolAddress and only those are handed to kernels.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[FGATTN_NOALLOC_SCRATCH_BYTES];
+static __device__ __align__(256) int g_noalloc_err_word;
+
+namespace {
+struct NoAllocAddrs {
+  void* scratch = nullptr;
+  int* err = nullptr;
+};
+NoAllocAddrs g_noalloc_addrs[64];
+
+// First use on a device: resolve the device addresses of the built-in arrays (no allocation).
+int noalloc_addrs(NoAllocAddrs* out) {
+  int dev = 0;
+  FG_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FGATTN_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  NoAllocAddrs& a = g_noalloc_addrs[dev];
+  if (!a.scratch) {
+    void* sp = nullptr;
+    void* ep = nullptr;
+    FG_CUDA(cudaGetSymbolAddress(&sp, g_noalloc_scratch));
+    FG_CUDA(cudaGetSymbolAddress(&ep, g_noalloc_err_word));
+    a.err = static_cast<int*>(ep);
+    a.scratch = sp;
+  }
+  // prefer the word fgattn_check reads when an earlier call already created it
+  out->scratch = a.scratch;
+  out->err = g_err_word[dev] ? g_err_word[dev] : a.err;
+  return FGATTN_OK;
+}
+}  // namespace
+
+int fgattn_block_index_lists_noalloc(int* kb_indices, int* kb_counts, int list_stride, float* max_q, float* denom,
+                                     void* o, const void* q, const void* k, const void* v, float threshold,
+                                     int batch, int heads, int seq, int D, int kv_seq_len, float scale, void* stream) {
+  if (!kb_indices || !kb_counts || !max_q || !denom || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
+  if ((o == nullptr) != (v == nullptr)) return FGATTN_INVALID_ARGUMENT;
+  if (o && !aligned16(o)) return FGATTN_MISALIGNED;
+  int r = check_qk(q, k, batch, heads, seq, D, kv_seq_len);
+  if (r) return r;
+  if (v && !aligned16(v)) return FGATTN_MISALIGNED;
+  const int nkb = (kv_seq_len + 63) / 64, nqb = (seq + 63) / 64, s_pad = ((seq + 127) / 128) * 128;
+  if (list_stride < nkb) return FGATTN_INVALID_ARGUMENT;
+  // reject sizes beyond the built-in maximum before anything is launched
+  const size_t per_head = size_t(nkb) * s_pad * sizeof(float);
+  if (per_head > size_t(FGATTN_NOALLOC_SCRATCH_BYTES)) return FGATTN_SCRATCH_TOO_SMALL;
+  const int chunk = int(std::min<size_t>(size_t(FGATTN_NOALLOC_SCRATCH_BYTES) / per_head, size_t(batch) * heads));
+  NoAllocAddrs addrs;
+  r = noalloc_addrs(&addrs);
+  if (r) return r;
+  DenseSetup s;
+  if (fg::make_qkv_map(&s.mq, q, batch * heads, seq, D, 128) || fg::make_qkv_map(&s.mk, k, batch * heads, seq, D, 128) ||
+      fg::make_qkv_map(&s.mv, v ? v : k, batch * heads, seq, D, 128))
+    return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
+  memset(&s.p, 0, sizeof(s.p));
+  s.p.S = seq;
+  s.p.S_pad = s_pad;
+  s.p.kv_len = kv_seq_len;
+  s.p.n_kv_tiles = (kv_seq_len + 127) / 128;
+  s.p.nkb = nkb;
+  s.p.scale_log2 = resolve_scale_log2(scale, D);
+  s.p.err = addrs.err;
+  s.p.o = static_cast<__nv_bfloat16*>(o);
+  s.p.max_q = max_q;
+  s.p.denom = denom;
+  s.p.blockmax = static_cast<float*>(addrs.scratch);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float log2_tau = log2f(threshold);
+  const int total = batch * heads;
+  for (int bh0 = 0; bh0 < total; bh0 += chunk) {
+    const int n = std::min(chunk, total - bh0);
+    s.p.bh0 = bh0;
+    r = o ? launch_dense<fg::kFullML, true>(D, s.mq, s.mk, s.mv, s.p, n, st)
+          : launch_dense<fg::kML, true>(D, s.mq, s.mk, s.mv, s.p, n, st);
+    if (r) return r;
+    const int smem = 64 * int(sizeof(float)) + ((nkb + 15) / 16) * 16;
+    fg::block_threshold_compact_kernel<<<dim3(nqb, n), 256, smem, st>>>(
+        s.p.blockmax, max_q, denom, kb_indices, kb_counts, seq, s_pad, nqb, nkb, list_stride, bh0, s.p.scale_log2,
+        log2_tau);
+    FG_CUDA(cudaGetLastError());
+  }
+  return FGATTN_OK;
+}
+
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq) {
   if (batch <= 0 || heads <= 0 || seq <= 0) return 0;
   const size_t npairs = size_t((seq + 127) / 128);

@@ -113,6 +113,32 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
                              int seq, int D, int kv_seq_len, float scale, void* scratch, size_t scratch_bytes,
                              void* stream);
 
+/* Largest scratch the library itself can lend: see fgattn_block_index_lists_noalloc. */
+#define FGATTN_NOALLOC_SCRATCH_BYTES (64u << 20)
+
+/* fgattn_block_index_lists for callers that are not allowed to touch the CUDA allocator at all.
+ * (No counterpart in the reference: every reference entry point leaves allocation to PyTorch.)
+ * Who needs this: code that runs inside a region where cudaMalloc is off limits -- the enqueue hook of
+ * an inference-engine plugin, a latency-critical serving loop whose device memory was carved up once
+ * at start-up, a host framework that forbids (or would serialise the whole device on) an allocation.
+ * Such a caller still owns q, k, v, the lists and max_q / denom, but has nowhere to get the
+ * block-maxima scratch from, so here the scratch is a 64 MiB array that lives inside the library
+ * image (FGATTN_NOALLOC_SCRATCH_BYTES; every GPU that loads the library holds it until the process
+ * exits).  One (batch, head) unit needs ceil(kv_seq_len/64) * ceil(seq/128)*128 * 4 bytes of it, so a
+ * unit up to seq = kv_seq_len = 32768 fits; units are processed in as many head chunks as needed, and
+ * a unit that does not fit returns FGATTN_SCRATCH_TOO_SMALL without launching anything.
+ * Same arguments and results as fgattn_block_index_lists, minus the scratch pointer.  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine; bounded-wait time-outs go to the error
+ * word that fgattn_check reads if some earlier call created it, else to a word inside the library.
+ * The first call on a device looks up the device address of the built-in array (once per device,
+ * with that device current); make that first call outside any stream capture.
+ * All calls share the one array and it keeps whatever the last call left in it (nothing in it needs
+ * clearing: each call overwrites what it reads); two calls that overlap on the GPU -- different
+ * streams, or different host threads -- race on it and must be serialised by the caller. */
+int fgattn_block_index_lists_noalloc(int* kb_indices, int* kb_counts, int list_stride, float* max_q, float* denom,
+                                     void* o, const void* q, const void* k, const void* v, float threshold,
+                                     int batch, int heads, int seq, int D, int kv_seq_len, float scale, void* stream);
+
 /* Block-sparse attention with the precomputed (max_q, denom) of the softmax over ALL keys: rows
  * of query block qb attend to the listed key blocks only, probabilities are not renormalised
  * (the masked attention of python/test_mask.py:37-54).  The gather of K/V tiles by index replaces
