@@ -496,9 +496,14 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
   int dev = 0, sms = 0;
   FG_CUDA(cudaGetDevice(&dev));
   FG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (p.npairs * int(sizeof(int)) > 48 * 1024) return FGATTN_UNSUPPORTED;
-  fg::sparse_order_kernel<<<batch * heads, 256, p.npairs * sizeof(int), st>>>(kb_counts, static_cast<int*>(workspace) + 4,
-                                                                          p.queue, p.nqb, p.npairs);
+  // heads per queue group: enough items to balance the SMs (about six per SM), K/V of a group <= 64 MiB
+  const int n_units = batch * heads;
+  const size_t kv_bytes_per_unit = size_t(4) * seq * D;
+  int group_heads = (6 * sms + p.npairs - 1) / p.npairs;
+  group_heads = std::min<int>(group_heads, int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit)));
+  group_heads = std::max(1, std::min(group_heads, n_units));
+  fg::sparse_order_kernel<<<(n_units + group_heads - 1) / group_heads, 256, 0, st>>>(
+      kb_counts, static_cast<int*>(workspace) + 4, p.queue, p.nqb, p.npairs, n_units, group_heads);
   FG_CUDA(cudaGetLastError());
   const int grid = std::min(p.n_items, sms);
   if (D == 128) {

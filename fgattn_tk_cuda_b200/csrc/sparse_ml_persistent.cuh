@@ -2,9 +2,9 @@
 //
 // Work item = one PAIR of neighbouring 64-row query blocks (one 128-row UMMA tile) of one
 // (batch, head) unit, walking the sorted union of the pair's two key-block lists, two listed key
-// blocks (128 keys) per step.  CTAs are persistent and pull items from a global queue; within a
-// head the queue is ordered longest-list-first, heads stay contiguous so that the K/V tiles being
-// gathered by the CTAs in flight fit in L2.
+// blocks (128 keys) per step.  CTAs are persistent and pull items from a global queue; heads are
+// queued in small groups (their K/V fits in L2) and inside a group the items are ordered
+// longest-list-first.
 //
 // Because the probabilities are p = 2^(s*c - (m*c + log2 l)) with m, l given, no row reduction is
 // needed and the two softmax warpgroups split the COLUMNS of a score tile (keys 0-63 / 64-127, i.e.
@@ -38,7 +38,7 @@ struct SparseMLParams {
   const float* denom;        // [BH, S_pad]
   const int* kb_idx;         // [BH, nqb, list_stride]
   const int* kb_cnt;         // [BH, nqb]
-  const int* order;          // [BH, npairs] pair indices, longest list first
+  const int* order;          // [BH * npairs] item ids (unit * npairs + pair) in queue order
   int* queue;                // global item counter (zeroed before the launch)
   int* err;
   int S, S_pad, kv_len, nqb, nkb, npairs, n_items, list_stride, list_cap;
@@ -212,8 +212,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         }
         break;
       }
-      const int bh = g / p.npairs;
-      const int pair = p.order[size_t(bh) * p.npairs + (g - bh * p.npairs)];
+      const int item = p.order[g];
+      const int bh = item / p.npairs;
+      const int pair = item - bh * p.npairs;
       for (int w = lane; w < 2 * words; w += 32) bm0[w] = 0u;
       __syncwarp();
       // both halves' counts are fetched before either list is walked
@@ -586,28 +587,57 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
   }
 }
 
-// Per head: order the query-block pairs by list length, longest first (rank by counting).
-// grid (BH), 256 threads, dynamic shared memory npairs ints.  Block 0 also clears the queue counter.
+// Queue order.  Heads are taken in groups of `group_heads` consecutive (batch, head) units (few
+// enough that the K/V of one group stays in L2, many enough that a group has several items per SM);
+// inside a group all query-block pairs are ordered longest list first, so that the long items start
+// early and the tail of the launch is made of short ones.  order[] receives global item ids
+// (unit * npairs + pair).  Counting sort on the list length; ties land in arbitrary order, which only
+// affects scheduling.  grid (number of groups), 256 threads.  Block 0 also clears the queue counter.
 __global__ void __launch_bounds__(256)
 sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int* __restrict__ queue, int nqb,
-                    int npairs) {
-  extern __shared__ int len[];
-  const int bh = blockIdx.x;
-  if (bh == 0 && threadIdx.x == 0) *queue = 0;
-  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
-    const int a = kb_cnt[size_t(bh) * nqb + 2 * i];
-    const int b = (2 * i + 1 < nqb) ? kb_cnt[size_t(bh) * nqb + 2 * i + 1] : 0;
-    len[i] = a + b;
+                    int npairs, int n_units, int group_heads) {
+  constexpr int kBuckets = 1024;
+  __shared__ int hist[kBuckets];
+  __shared__ int part[256];
+  const int tid = threadIdx.x;
+  const int u0 = blockIdx.x * group_heads, u1 = min(n_units, u0 + group_heads);
+  const int n = (u1 - u0) * npairs;
+  if (blockIdx.x == 0 && tid == 0) *queue = 0;
+  for (int i = tid; i < kBuckets; i += 256) hist[i] = 0;
+  __syncthreads();
+  auto length_of = [&](int i) {
+    const int unit = u0 + i / npairs, pair = i % npairs;
+    const int a = kb_cnt[size_t(unit) * nqb + 2 * pair];
+    const int b = (2 * pair + 1 < nqb) ? kb_cnt[size_t(unit) * nqb + 2 * pair + 1] : 0;
+    return min(max(a + b, 0), kBuckets - 1);
+  };
+  for (int i = tid; i < n; i += 256) atomicAdd(&hist[length_of(i)], 1);
+  __syncthreads();
+  // start[b] = number of items in longer buckets; thread t owns buckets (1023 - 4t) .. (1020 - 4t)
+  int local[4], sum = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    local[j] = hist[kBuckets - 1 - (4 * tid + j)];
+    sum += local[j];
+  }
+  part[tid] = sum;
+  __syncthreads();
+  for (int off = 1; off < 256; off <<= 1) {
+    const int v = (tid >= off) ? part[tid - off] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  int run = part[tid] - sum;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    hist[kBuckets - 1 - (4 * tid + j)] = run;
+    run += local[j];
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
-    const int li = len[i];
-    int rank = 0;
-    for (int j = 0; j < npairs; ++j) {
-      const int lj = len[j];
-      rank += (lj > li || (lj == li && j < i)) ? 1 : 0;
-    }
-    order[size_t(bh) * npairs + rank] = i;
+  for (int i = tid; i < n; i += 256) {
+    const int pos = atomicAdd(&hist[length_of(i)], 1);
+    order[size_t(u0) * npairs + pos] = u0 * npairs + i;
   }
 }
 
