@@ -231,6 +231,9 @@ def main():
     scratch = spattn.mask_utils._block_scratch(q)
     ms_full = ev_time(lambda: capi.full_attn(o, q, k, v), 5, 2)
     ms_lists = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch), 5, 2)
+    ms_maxq = ev_time(lambda: capi.maxq_denom(max_q, denom, q, k), 5, 2)
+    s_pad = 128 * ((S + 127) // 128)
+    mask_bytes = B * H * (4.0 * s_pad * nkb * 2 + 8.0 * S + 4.0 * nqb * nkb + 4.0 * nqb)
     ms_build = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch, o=o, v=v), 5, 2)
 
     step = lambda: torch.ops.cuda_attn.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
@@ -298,7 +301,7 @@ def main():
                     "api": "spattn.sparseattn_functionals.cached_attn_cuda (sparse step from cached lists)"},
             "gpu_launches": args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "sparse_block_attn_kernel<128,false>", "achieved": achieved,
+            "roofline": {"bound": "tensor", "kernel": "sparse_ml_persistent_kernel<128>", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16_tflops (burst: kernel timed alone)",
                          "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "traffic": None},
@@ -306,15 +309,19 @@ def main():
                 "full_attn_ms": ms_full, "full_attn_tflops": F_full / ms_full / 1e9,
                 "full_attn_frac_of_peak": F_full / ms_full / 1e9 / peak,
                 "block_lists_ms": ms_lists, "block_lists_qk_tflops": F_full / 2 / ms_lists / 1e9,
+                "maxq_denom_ms": ms_maxq, "maxq_denom_qk_tflops": F_full / 2 / ms_maxq / 1e9,
+                "mask_epilogue_ms": ms_lists - ms_maxq,
+                "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
+                "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
                 "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
                 "sparse_ms": ms_step, "sparse_speedup_over_full": ms_full / ms_step,
                 "ideal_speedup_1_over_density": 1.0 / density,
                 "speedup_gap": (1.0 / density) / (ms_full / ms_step)},
         }
         # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
-        # profiles/sparse_block_attn_c3_16heads.md (16 heads: 271 MB), scaled by heads
+        # profiles/sparse_ml_persistent_c3_16heads.md (16 heads: 305 MB), scaled by heads
         if args.workload == "c3":
-            line["roofline"]["traffic"] = 271.0e6 * (w.B * w.H) / 16.0
+            line["roofline"]["traffic"] = 305.0e6 * (w.B * w.H) / 16.0
         if world == 1 and not args.no_cpu_baseline:
             r = run_cpu(w, steps=2, warmup=1, budget_s=25.0)
             line["cpu_baseline"] = {k_: r[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}

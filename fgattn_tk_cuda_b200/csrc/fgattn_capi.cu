@@ -501,6 +501,7 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
   const size_t kv_bytes_per_unit = size_t(4) * seq * D;
   int group_heads = (6 * sms + p.npairs - 1) / p.npairs;
   group_heads = std::min<int>(group_heads, int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit)));
+  if (const char* gh = getenv("FGATTN_GROUP_HEADS")) group_heads = atoi(gh);   // tuning override
   group_heads = std::max(1, std::min(group_heads, n_units));
   fg::sparse_order_kernel<<<(n_units + group_heads - 1) / group_heads, 256, 0, st>>>(
       kb_counts, static_cast<int*>(workspace) + 4, p.queue, p.nqb, p.npairs, n_units, group_heads);
