@@ -4,6 +4,10 @@
 #pragma once
 #include "sm100_ptx.cuh"
 
+#ifndef FG_DENSE_POLY_OF8
+#define FG_DENSE_POLY_OF8 0      // of every 8 column pairs, how many use the polynomial exp2
+#endif
+
 namespace fg {
 
 struct OnlineState {
@@ -92,8 +96,13 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
   const float neg_m = -st.m_used;
 #pragma unroll
   for (int i = 0; i < 128; i += 2) {
-    const float p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
-    const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+    float p0, p1;
+    if (((i >> 1) & 7) < FG_DENSE_POLY_OF8) {        // part of the exponentials on the FMA pipe
+      ex2_poly2(fmaf(__uint_as_float(r[i]), c, neg_m), fmaf(__uint_as_float(r[i + 1]), c, neg_m), p0, p1);
+    } else {
+      p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
+      p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+    }
     sum0 += p0;
     sum1 += p1;
     if (WRITE_P) r[i >> 1] = pack_bf16(p0, p1);

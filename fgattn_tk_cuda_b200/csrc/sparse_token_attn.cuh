@@ -120,13 +120,16 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       if (f > 0) ok = mbar_wait(bar(TB_EMPTY + st), (f - 1) & 1, ab, p.err, 701);
       if (!ok) return;
       const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
-      for (int c = gtid; c < 128 * kChunksPerRow; c += Cfg::kGatherThreads) {
-        const int row = c / kChunksPerRow, ch = c % kChunksPerRow;
+      // one thread per gathered row: the index is read once, then the row's 16-byte chunks follow
+      // (measured faster than 16 lanes per row, where every copy waits for its own index load)
+      for (int row = gtid; row < 128; row += Cfg::kGatherThreads) {
         const int pos = j * 128 + row;
         int tok = (pos < cnt[t]) ? lst[t][pos] : 0;
         if (tok < 0 || tok >= p.S) tok = 0;                            // masked column: any finite row will do
-        const __nv_bfloat16* src = base + (size_t(bh) * p.S + tok) * D + ch * 8;
-        cp_async_16(dst + (ch >> 3) * 16384 + sw128_offset(row, ch & 7), src);
+        const __nv_bfloat16* src = base + (size_t(bh) * p.S + tok) * D;
+#pragma unroll
+        for (int ch = 0; ch < kChunksPerRow; ++ch)
+          cp_async_16(dst + (ch >> 3) * 16384 + sw128_offset(row, ch & 7), src + ch * 8);
       }
       cp_async_commit();
       if (pending_stage >= 0) {
