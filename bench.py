@@ -174,7 +174,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     config = {"workload": w.name, "B": w.B, "H": w.H, "S": w.S, "D": w.D, "block": "64x64", "tau": w.tau,
               "units_per_gpu": f"{w.B * w.H} (batch x head) units", "partition": f"replicated workload x{world}, "
-              "disjoint head seeds per rank, no collective", "l2": "inputs (512 MiB) larger than L2, no flush"}
+              "disjoint head seeds per rank, no collective", "l2": f"inputs ({4 * w.B * w.H * w.S * w.D * 2 >> 20} MiB of q,k,v,o) larger than L2, no flush"}
 
     if args.impl == "reference":
         if rank != 0:

@@ -16,6 +16,10 @@ struct OnlineState {
   float l;        // running denominator relative to m_used
 };
 
+// exponent (log2 domain, relative to the running maximum) below which a whole 32-column quarter
+// is treated as zero by softmax_online_step
+constexpr float kSkipLog2 = -40.0f;
+
 __device__ __forceinline__ void online_init(OnlineState& st) {
   st.m_used = -1.0e30f;
   st.m_true = -INFINITY;
@@ -63,13 +67,17 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
       }
     }
   }
-  mx0 = __uint_as_float(r[0]);
-  mx1 = __uint_as_float(r[64]);
+  // maxima of the four 32-column quarters (four independent chains)
+  float qmax[4];
 #pragma unroll
-  for (int i = 1; i < 64; ++i) {
-    mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-    mx1 = fmaxf(mx1, __uint_as_float(r[64 + i]));
+  for (int w = 0; w < 4; ++w) qmax[w] = __uint_as_float(r[w * 32]);
+#pragma unroll
+  for (int i = 1; i < 32; ++i) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) qmax[w] = fmaxf(qmax[w], __uint_as_float(r[w * 32 + i]));
   }
+  mx0 = fmaxf(qmax[0], qmax[1]);
+  mx1 = fmaxf(qmax[2], qmax[3]);
   const float mx = fmaxf(mx0, mx1);
   st.m_true = fmaxf(st.m_true, mx);
   const float ms = mx * c;
@@ -95,17 +103,32 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
   float sum0 = 0.f, sum1 = 0.f;
   const float neg_m = -st.m_used;
 #pragma unroll
-  for (int i = 0; i < 128; i += 2) {
-    float p0, p1;
-    if (((i >> 1) & 7) < FG_DENSE_POLY_OF8) {        // part of the exponentials on the FMA pipe
-      ex2_poly2(fmaf(__uint_as_float(r[i]), c, neg_m), fmaf(__uint_as_float(r[i + 1]), c, neg_m), p0, p1);
-    } else {
-      p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
-      p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+  for (int w = 0; w < 4; ++w) {
+    // A quarter whose largest exponent is below kSkipLog2 for every row of the warp contributes
+    // less than 2^-40 per entry relative to the running maximum -- under one fp32 ulp of the
+    // denominator and of the output even summed over a whole row -- so its exponentials are
+    // skipped and its probabilities are exact zeros.
+    const bool skip = __all_sync(0xffffffffu, fmaf(qmax[w], c, neg_m) < kSkipLog2);
+    if (skip) {
+      if (WRITE_P) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[w * 16 + i] = 0u;
+      }
+      continue;
     }
-    sum0 += p0;
-    sum1 += p1;
-    if (WRITE_P) r[i >> 1] = pack_bf16(p0, p1);
+#pragma unroll
+    for (int i = w * 32; i < w * 32 + 32; i += 2) {
+      float p0, p1;
+      if (((i >> 1) & 7) < FG_DENSE_POLY_OF8) {      // part of the exponentials on the FMA pipe
+        ex2_poly2(fmaf(__uint_as_float(r[i]), c, neg_m), fmaf(__uint_as_float(r[i + 1]), c, neg_m), p0, p1);
+      } else {
+        p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
+        p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+      }
+      sum0 += p0;
+      sum1 += p1;
+      if (WRITE_P) r[i >> 1] = pack_bf16(p0, p1);
+    }
   }
   st.l += sum0 + sum1;
   if (WRITE_P) {

@@ -197,10 +197,12 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     reg_dealloc<Cfg::kRegsService>();
     uint32_t* bm0 = bitmaps;
     uint32_t* bm1 = bitmaps + words;
-    for (int it = 0;; ++it) {
+    long long w_le = 0, t_start = FG_CLK();
+    int it = 0;
+    for (;; ++it) {
       const int lb = it % NLB;
       bool ok = true;
-      if (it >= NLB) ok = mbar_wait(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001);
+      if (it >= NLB) FG_TW(w_le, ok = mbar_wait(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001));
       if (!ok) break;
       int g = 0;
       if (lane == 0) g = atomicAdd(p.queue, 1);
@@ -275,6 +277,10 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         mbar_arrive(bar(PB_LIST_FULL + lb));
       }
       __syncwarp();
+    }
+    if (p.stats && lane == 0) {
+      long long* st_ = p.stats + size_t(blockIdx.x) * 32;
+      st_[5] = FG_CLK() - t_start; st_[6] = w_le; st_[7] = it;
     }
   } else if (warp == Cfg::kWarpProdK || warp == Cfg::kWarpProdV) {
     // ------------------------------------------------------------------ TMA producers
