@@ -299,7 +299,7 @@ def main():
             "e2e": {"value": F_total / ms_e2e_all / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_all,
                     "api": "spattn.sparseattn_functionals.cached_attn_cuda (sparse step from cached lists)"},
-            "gpu_launches": args.steps,
+            "gpu_launches": 2 * args.steps,          # per step: sparse_order_kernel + sparse_ml_persistent_kernel
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "sparse_ml_persistent_kernel<128>", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
