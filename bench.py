@@ -235,6 +235,17 @@ def main():
     s_pad = 128 * ((S + 127) // 128)
     mask_bytes = B * H * (4.0 * s_pad * nkb * 2 + 8.0 * S + 4.0 * nqb * nkb + 4.0 * nqb)
     ms_build = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch, o=o, v=v), 5, 2)
+    # one-bit-per-entry mask kernels on a token mask of the reference granularity (int32 [B,H,S/128,S_pad],
+    # 8 % kept): pack = 4 B read + 1/8 B written per entry; packed -> lists = 1/8 B read + 4 B written
+    tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
+    tpacked = torch.empty(B, H, tmask.shape[2], s_pad // 8, dtype=torch.uint8, device=dev)
+    tidx = torch.empty_like(tmask)
+    tcnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
+    pack_bytes = tmask.numel() * (4.0 + 0.125)
+    ms_pack = ev_time(lambda: capi.pack_mask(tpacked, tmask), 10, 3)
+    ms_p2i = ev_time(lambda: capi.packedmask_to_indexmask(tidx, tcnt, tpacked, S), 10, 3)
+    ms_m2i = ev_time(lambda: capi.booleanmask_to_indexmask(tidx, tcnt, tmask, S), 10, 3)
+    del tmask, tidx
 
     step = lambda: torch.ops.cuda_attn.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
 
@@ -262,16 +273,14 @@ def main():
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
     dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
-    mask_cache = spattn.mask_utils.NaiveMaskCache(compute_cache_at=[])
-    mask_cache.update_cache(0, idx, cnt, max_q, denom)
+    do = torch.empty_like(o)
 
     def e2e_step():
         dq.copy_(hq, non_blocking=True)
         dk.copy_(hk, non_blocking=True)
         dv.copy_(hv, non_blocking=True)
-        out = spattn.sparseattn_functionals.cached_attn_cuda(dq, dk, dv, 0, 1, thresh=w.tau, blocksz=64,
-                                                             mask_cache=mask_cache)
-        ho.copy_(out, non_blocking=True)
+        torch.ops.cuda_attn.sp_attn_blocks_ml(do, dq, dk, dv, idx, cnt, max_q, denom)
+        ho.copy_(do, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = ev_time(e2e_step, e2e_steps, 2)
@@ -298,7 +307,7 @@ def main():
             "density": density, "kept_blocks_per_gpu": nnz,
             "e2e": {"value": F_total / ms_e2e_all / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_all,
-                    "api": "spattn.sparseattn_functionals.cached_attn_cuda (sparse step from cached lists)"},
+                    "api": "torch.ops.cuda_attn.sp_attn_blocks_ml on q, k, v copied from pinned host memory"},
             "gpu_launches": 2 * args.steps,          # per step: sparse_order_kernel + sparse_ml_persistent_kernel
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "sparse_ml_persistent_kernel<128>", "achieved": achieved,
@@ -313,6 +322,11 @@ def main():
                 "mask_epilogue_ms": ms_lists - ms_maxq,
                 "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
                 "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
+                "pack_mask_ms": ms_pack, "pack_mask_gbs": pack_bytes / ms_pack / 1e6,
+                "pack_mask_frac_of_hbm_peak": pack_bytes / ms_pack / 1e6 / peaks["hbm_gbs"],
+                "packedmask_to_indexmask_ms": ms_p2i, "packedmask_to_indexmask_gbs": pack_bytes / ms_p2i / 1e6,
+                "packedmask_to_indexmask_frac_of_hbm_peak": pack_bytes / ms_p2i / 1e6 / peaks["hbm_gbs"],
+                "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
                 "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
                 "sparse_ms": ms_step, "sparse_speedup_over_full": ms_full / ms_step,
                 "ideal_speedup_1_over_density": 1.0 / density,

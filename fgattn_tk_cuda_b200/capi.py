@@ -19,7 +19,7 @@ OK = 0
 STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "UNSUPPORTED", 3: "MISALIGNED", 4: "CUDA_ERROR", 5: "NO_DRIVER",
                 6: "DEVICE_TIMEOUT", 7: "SCRATCH_TOO_SMALL"}
 
-_vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+_vp, _i, _f, _sz, _ll = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_longlong
 
 # name -> (restype, argtypes); mirrors include/fgattn_b200.h one to one
 PROTOTYPES = {
@@ -42,6 +42,10 @@ PROTOTYPES = {
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
     "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_pack_mask": (_i, [_vp, _vp, _i, _ll, _i, _vp]),
+    "fgattn_unpack_mask": (_i, [_vp, _i, _vp, _ll, _i, _vp]),
+    "fgattn_packedmask_to_indexmask": (_i, [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp]),
+    "fgattn_indexmask_to_packedmask": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
 }
 
 _lib = None
@@ -206,3 +210,47 @@ def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn_blocks", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
               kb_indices.shape[3], B, H, S, D, kv_seq_len or S, scale, _stream(q))
+
+
+# ---- one-bit-per-entry masks ----------------------------------------------------------------------
+def _mask_elem_size(t: torch.Tensor) -> int:
+    if not t.is_cuda or not t.is_contiguous():
+        raise FgattnError("argument check", 1, "mask tensors must be contiguous CUDA tensors")
+    if t.dtype in (torch.bool, torch.uint8):
+        return 1
+    if t.dtype == torch.int32:
+        return 4
+    raise FgattnError("argument check", 1, "masks are bool, uint8 or int32")
+
+
+def pack_mask(packed, mask):
+    """mask [..., W] (bool / uint8 / int32, kept iff > 0) -> packed uint8 [..., W/8]."""
+    W = mask.shape[-1]
+    with torch.cuda.device(mask.device):
+        _call("fgattn_pack_mask", _ptr(packed), _ptr(mask), _mask_elem_size(mask), mask.numel() // W, W, _stream(mask))
+
+
+def unpack_mask(mask, packed):
+    """packed uint8 [..., W/8] -> mask [..., W] of 0 / 1 (bool / uint8 / int32)."""
+    W = mask.shape[-1]
+    with torch.cuda.device(mask.device):
+        _call("fgattn_unpack_mask", _ptr(mask), _mask_elem_size(mask), _ptr(packed), mask.numel() // W, W,
+              _stream(mask))
+
+
+def packedmask_to_indexmask(indices, num_indices, packed, n_valid, sentinel=None):
+    """packed uint8 [..., W/8] -> ascending lists `indices` int32 [..., stride] + counts [...]."""
+    W = packed.shape[-1] * 8
+    stride = indices.shape[-1]
+    with torch.cuda.device(packed.device):
+        _call("fgattn_packedmask_to_indexmask", _ptr(indices), _ptr(num_indices), _ptr(packed),
+              packed.numel() // packed.shape[-1], W, stride, int(n_valid), stride if sentinel is None else int(sentinel),
+              _stream(packed))
+
+
+def indexmask_to_packedmask(packed, indices, num_indices):
+    """lists int32 [..., stride] + counts [...] -> packed uint8 [..., W/8]."""
+    W = packed.shape[-1] * 8
+    with torch.cuda.device(packed.device):
+        _call("fgattn_indexmask_to_packedmask", _ptr(packed), _ptr(indices), _ptr(num_indices),
+              packed.numel() // packed.shape[-1], indices.shape[-1], W, _stream(packed))

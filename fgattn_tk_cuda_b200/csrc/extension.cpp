@@ -143,6 +143,59 @@ void sp_attn_blocks(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Te
                "sp_attn_blocks");
 }
 
+// ---- one-bit-per-entry masks (additions) ---------------------------------------------------------
+int mask_elem_size(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  if (t.scalar_type() == at::kBool || t.scalar_type() == at::kByte) return 1;
+  TORCH_CHECK(t.scalar_type() == at::kInt, name, " must be bool, uint8 or int32");
+  return 4;
+}
+
+void pack_mask(torch::Tensor packed, torch::Tensor mask) {
+  check_dtype(packed, at::kByte, "packed");
+  const int es = mask_elem_size(mask, "mask");
+  const int64_t W = mask.size(-1);
+  TORCH_CHECK(W % 8 == 0 && packed.numel() * 8 == mask.numel(), "packed must hold one bit per mask entry");
+  c10::cuda::CUDAGuard guard(mask.device());
+  check_status(fgattn_pack_mask(packed.data_ptr<uint8_t>(), mask.data_ptr(), es, mask.numel() / W, int(W),
+                                stream_of(mask)), "pack_mask");
+}
+
+void unpack_mask(torch::Tensor mask, torch::Tensor packed) {
+  check_dtype(packed, at::kByte, "packed");
+  const int es = mask_elem_size(mask, "mask");
+  const int64_t W = mask.size(-1);
+  TORCH_CHECK(W % 8 == 0 && packed.numel() * 8 == mask.numel(), "packed must hold one bit per mask entry");
+  c10::cuda::CUDAGuard guard(mask.device());
+  check_status(fgattn_unpack_mask(mask.data_ptr(), es, packed.data_ptr<uint8_t>(), mask.numel() / W, int(W),
+                                  stream_of(mask)), "unpack_mask");
+}
+
+void packedmask_to_indexmask(torch::Tensor indices, torch::Tensor num_indices, torch::Tensor packed, int64_t n_valid,
+                             int64_t sentinel) {
+  check_dtype(indices, at::kInt, "indices"); check_dtype(num_indices, at::kInt, "num_indices");
+  check_dtype(packed, at::kByte, "packed");
+  const int64_t rows = packed.numel() / packed.size(-1);
+  TORCH_CHECK(num_indices.numel() == rows && indices.numel() == rows * indices.size(-1), "row counts differ");
+  c10::cuda::CUDAGuard guard(packed.device());
+  check_status(fgattn_packedmask_to_indexmask(indices.data_ptr<int>(), num_indices.data_ptr<int>(),
+                                              packed.data_ptr<uint8_t>(), rows, int(packed.size(-1) * 8),
+                                              int(indices.size(-1)), int(n_valid), int(sentinel), stream_of(packed)),
+               "packedmask_to_indexmask");
+}
+
+void indexmask_to_packedmask(torch::Tensor packed, torch::Tensor indices, torch::Tensor num_indices) {
+  check_dtype(indices, at::kInt, "indices"); check_dtype(num_indices, at::kInt, "num_indices");
+  check_dtype(packed, at::kByte, "packed");
+  const int64_t rows = packed.numel() / packed.size(-1);
+  TORCH_CHECK(num_indices.numel() == rows && indices.numel() == rows * indices.size(-1), "row counts differ");
+  c10::cuda::CUDAGuard guard(packed.device());
+  check_status(fgattn_indexmask_to_packedmask(packed.data_ptr<uint8_t>(), indices.data_ptr<int>(),
+                                              num_indices.data_ptr<int>(), rows, int(indices.size(-1)),
+                                              int(packed.size(-1) * 8), stream_of(packed)),
+               "indexmask_to_packedmask");
+}
+
 int64_t block_scratch_bytes(int64_t batch, int64_t heads, int64_t seq, int64_t kv_seq_len) {
   return int64_t(fgattn_block_scratch_bytes(int(batch), int(heads), int(seq), int(kv_seq_len)));
 }
@@ -157,6 +210,9 @@ void meta8(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Te
            torch::Tensor) {}
 void meta_bil(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, c10::optional<torch::Tensor>, torch::Tensor,
               torch::Tensor, c10::optional<torch::Tensor>, double, torch::Tensor) {}
+void meta2(torch::Tensor, torch::Tensor) {}
+void meta3(torch::Tensor, torch::Tensor, torch::Tensor) {}
+void meta_p2i(torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t) {}
 
 }  // namespace
 
@@ -173,6 +229,11 @@ TORCH_LIBRARY_FRAGMENT(cuda_attn, m) {
   m.def("block_index_lists(Tensor (kb_indices!) kb_indices, Tensor (kb_counts!) kb_counts, Tensor (o_max_q!) o_max_q, Tensor (o_denom!) o_denom, Tensor(o!)? o, Tensor q, Tensor k, Tensor? v, float threshold, Tensor (scratch!) scratch) -> ()");
   m.def("sp_attn_blocks_ml(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts, Tensor max_q, Tensor denom) -> ()");
   m.def("sp_attn_blocks(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts) -> ()");
+  // one-bit-per-entry masks
+  m.def("pack_mask(Tensor (packed!) packed, Tensor mask) -> ()");
+  m.def("unpack_mask(Tensor (mask!) mask, Tensor packed) -> ()");
+  m.def("packedmask_to_indexmask(Tensor (indices!) indices, Tensor (num_indices!) num_indices, Tensor packed, int n_valid, int sentinel) -> ()");
+  m.def("indexmask_to_packedmask(Tensor (packed!) packed, Tensor indices, Tensor num_indices) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(cuda_attn, Meta, m) {
@@ -186,6 +247,10 @@ TORCH_LIBRARY_IMPL(cuda_attn, Meta, m) {
   m.impl("block_index_lists", meta_bil);
   m.impl("sp_attn_blocks_ml", meta8);
   m.impl("sp_attn_blocks", meta6);
+  m.impl("pack_mask", meta2);
+  m.impl("unpack_mask", meta2);
+  m.impl("packedmask_to_indexmask", meta_p2i);
+  m.impl("indexmask_to_packedmask", meta3);
 }
 
 TORCH_LIBRARY_IMPL(cuda_attn, CUDA, m) {
@@ -199,6 +264,10 @@ TORCH_LIBRARY_IMPL(cuda_attn, CUDA, m) {
   m.impl("block_index_lists", block_index_lists);
   m.impl("sp_attn_blocks_ml", sp_attn_blocks_ml);
   m.impl("sp_attn_blocks", sp_attn_blocks);
+  m.impl("pack_mask", pack_mask);
+  m.impl("unpack_mask", unpack_mask);
+  m.impl("packedmask_to_indexmask", packedmask_to_indexmask);
+  m.impl("indexmask_to_packedmask", indexmask_to_packedmask);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -213,4 +282,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sp_attn_blocks_ml", &sp_attn_blocks_ml, "block-sparse attention, precomputed m/l");
   m.def("sp_attn_blocks", &sp_attn_blocks, "block-sparse attention, renormalising");
   m.def("block_scratch_bytes", &block_scratch_bytes, "scratch bytes for block_index_lists");
+  m.def("pack_mask", &pack_mask, "mask -> one bit per entry");
+  m.def("unpack_mask", &unpack_mask, "one bit per entry -> mask");
+  m.def("packedmask_to_indexmask", &packedmask_to_indexmask, "packed mask -> ascending index lists");
+  m.def("indexmask_to_packedmask", &indexmask_to_packedmask, "index lists -> packed mask");
 }

@@ -8,6 +8,7 @@
 #include "../../include/fgattn_b200.h"
 #include "dense_attn.cuh"
 #include "mask_kernels.cuh"
+#include "packed_mask.cuh"
 #include "sparse_attn.cuh"
 #include "sparse_ml_persistent.cuh"
 #include "sparse_token_attn.cuh"
@@ -522,6 +523,65 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
     if (r) return r;
     kern<<<grid, fg::SparseMLCfg<64>::kThreads, smem, st>>>(mq, mk, mv, p);
   }
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+// ---- one-bit-per-entry masks -------------------------------------------------------------------
+namespace {
+int byte_grid(long long n_bytes) { return int(std::min<long long>((n_bytes + 255) / 256, 148LL * 64)); }
+}  // namespace
+
+int fgattn_pack_mask(unsigned char* packed, const void* mask, int elem_size, long long rows, int width, void* stream) {
+  if (!packed || !mask || rows <= 0 || width <= 0) return FGATTN_INVALID_ARGUMENT;
+  if (elem_size != 1 && elem_size != 4) return FGATTN_UNSUPPORTED;
+  if (width % 8) return FGATTN_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(mask) & (elem_size == 4 ? 15u : 7u)) return FGATTN_MISALIGNED;
+  const long long n_bytes = rows * (width / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (elem_size == 4)
+    fg::pack_mask_kernel<int><<<byte_grid(n_bytes), 256, 0, st>>>(static_cast<const int*>(mask), packed, n_bytes);
+  else
+    fg::pack_mask_kernel<uint8_t><<<byte_grid(n_bytes), 256, 0, st>>>(static_cast<const uint8_t*>(mask), packed, n_bytes);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+int fgattn_unpack_mask(void* mask, int elem_size, const unsigned char* packed, long long rows, int width, void* stream) {
+  if (!packed || !mask || rows <= 0 || width <= 0) return FGATTN_INVALID_ARGUMENT;
+  if (elem_size != 1 && elem_size != 4) return FGATTN_UNSUPPORTED;
+  if (width % 8) return FGATTN_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(mask) & (elem_size == 4 ? 15u : 7u)) return FGATTN_MISALIGNED;
+  const long long n_bytes = rows * (width / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (elem_size == 4)
+    fg::unpack_mask_kernel<int><<<byte_grid(n_bytes), 256, 0, st>>>(packed, static_cast<int*>(mask), n_bytes);
+  else
+    fg::unpack_mask_kernel<uint8_t><<<byte_grid(n_bytes), 256, 0, st>>>(packed, static_cast<uint8_t*>(mask), n_bytes);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+int fgattn_packedmask_to_indexmask(int* indices, int* num_indices, const unsigned char* packed, long long rows,
+                                   int width, int list_stride, int n_valid, int sentinel, void* stream) {
+  if (!indices || !num_indices || !packed) return FGATTN_INVALID_ARGUMENT;
+  if (rows <= 0 || width <= 0 || list_stride <= 0 || n_valid < 0 || width % 8) return FGATTN_INVALID_ARGUMENT;
+  if (rows > 2147483647LL) return FGATTN_UNSUPPORTED;
+  fg::packed_to_index_kernel<<<unsigned(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      packed, width / 8, indices, num_indices, list_stride, std::min(n_valid, width), sentinel);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, const int* num_indices, long long rows,
+                                   int list_stride, int width, void* stream) {
+  if (!indices || !num_indices || !packed) return FGATTN_INVALID_ARGUMENT;
+  if (rows <= 0 || width <= 0 || list_stride <= 0 || width % 8) return FGATTN_INVALID_ARGUMENT;
+  if (rows > 2147483647LL) return FGATTN_UNSUPPORTED;
+  const int row_bytes = width / 8, smem = ((row_bytes + 3) / 4) * 4;
+  if (smem > 48 * 1024) return FGATTN_UNSUPPORTED;        // rows of up to 393216 entries
+  fg::index_to_packed_kernel<<<unsigned(rows), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      indices, num_indices, list_stride, packed, row_bytes, width);
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;
 }

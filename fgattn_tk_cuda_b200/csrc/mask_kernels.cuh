@@ -61,6 +61,19 @@ block_threshold_compact_kernel(const float* __restrict__ blockmax, const float* 
   for (int i = count + tid; i < list_stride; i += 256) out[i] = nkb;
 }
 
+// dst[from .. n) = value by the 256 threads of a CTA: 16-byte stores where the row allows it.
+__device__ __forceinline__ void fill_tail(int* __restrict__ dst, int from, int n, int value, int tid) {
+  if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    const int a = min(n, (from + 3) & ~3), b = n & ~3;       // [from,a) scalar, [a,b) vector, [b,n) scalar
+    if (tid < a - from) dst[from + tid] = value;
+    const int4 v4 = make_int4(value, value, value, value);
+    for (int i = a + 4 * tid; i < b; i += 1024) *reinterpret_cast<int4*>(dst + i) = v4;
+    if (b >= a && tid < n - b) dst[b + tid] = value;
+  } else {
+    for (int i = from + tid; i < n; i += 256) dst[i] = value;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Mask row -> ascending index list + count (deterministic replacement of an atomic-ticket scan).
 // mask int32 [rows, stride], entry kept iff mask > 0 and column < n_valid.  Unused list slots are
@@ -115,7 +128,7 @@ mask_to_index_kernel(const int* __restrict__ mask, int* __restrict__ idx, int* _
   }
   const int total = s_base;
   if (tid == 0) cnt[blockIdx.x] = total;
-  for (int i = total + tid; i < stride; i += 256) dst[i] = stride;
+  fill_tail(dst, min(total, stride), stride, stride, tid);
 }
 
 // Identity lists: idx[row][s] = s for every slot, count = n_keep.

@@ -65,29 +65,65 @@ class BitMaskCache(NaiveMaskCache):
 
 
 class CompressedBitMaskCache(BitMaskCache):
-    """Same, with the mask packed to one bit per entry (pack / unpack below)."""
+    """Same, with the mask packed to one bit per entry (python/spattn/mask_utils.py:87-98).  Reading
+    goes from the packed bits straight to the lists in one kernel; the int32 mask is never rebuilt."""
 
     def get_mask_from_cache(self, layer):
         packed, seq_len = self.cache[layer]
-        return bitmask_to_indexmask_cuda(unpack(packed).to(torch.int32), seq_len)
+        return packedmask_to_indexmask_cuda(packed, seq_len)
 
     def update_cache(self, layer, mask, seq_len):
-        self.cache[layer] = (pack(mask > 0), seq_len)
+        self.cache[layer] = (pack(mask), seq_len)
 
 
-def pack(bool_tensor: torch.Tensor) -> torch.Tensor:
-    """bool [..., W] (W % 8 == 0) -> uint8 [..., W/8], least significant bit first
-    (python/spattn/mask_utils.py:421-430)."""
-    w = torch.tensor([1, 2, 4, 8, 16, 32, 64, 128], dtype=torch.uint8, device=bool_tensor.device)
-    g = bool_tensor.reshape(*bool_tensor.shape[:-1], bool_tensor.shape[-1] // 8, 8).to(torch.uint8)
-    return (g * w).sum(dim=-1).to(torch.uint8)
+class CompressedListCache(NaiveMaskCache):
+    """Caches index lists (key tokens or 64-key blocks) as one bit per entry: 1/32 of the int32 lists.
+    `width` = number of list targets (keys or key blocks); lists come back ascending, unused slots
+    filled with the list stride."""
+
+    def get_mask_from_cache(self, layer):
+        packed, width, stride = self.cache[layer]
+        return packedmask_to_indexmask_cuda(packed, width, stride=stride)
+
+    def update_cache(self, layer, indices, num_indices, width=None):
+        width = indices.shape[-1] if width is None else width
+        self.cache[layer] = (indexmask_to_packedmask_cuda(indices, num_indices, width), width, indices.shape[-1])
 
 
-def unpack(packed: torch.Tensor) -> torch.Tensor:
-    """Inverse of pack (python/spattn/mask_utils.py:433-440)."""
-    w = torch.tensor([1, 2, 4, 8, 16, 32, 64, 128], dtype=torch.uint8, device=packed.device)
-    bits = (packed.unsqueeze(-1) & w) != 0
-    return bits.reshape(*packed.shape[:-1], packed.shape[-1] * 8)
+def pack(mask: torch.Tensor) -> torch.Tensor:
+    """[..., W] (bool / uint8 / int32, kept iff > 0; W % 8 == 0) -> uint8 [..., W/8], least significant
+    bit first (python/spattn/mask_utils.py:421-430)."""
+    mask = mask.contiguous()
+    packed = torch.empty((*mask.shape[:-1], mask.shape[-1] // 8), dtype=torch.uint8, device=mask.device)
+    spattn_interface.pack_mask(packed, mask)
+    return packed
+
+
+def unpack(packed: torch.Tensor, dtype=torch.bool) -> torch.Tensor:
+    """Inverse of pack (python/spattn/mask_utils.py:433-440): bool [..., 8 * W8] (or uint8 / int32 of
+    0 / 1 when `dtype` says so)."""
+    packed = packed.contiguous()
+    mask = torch.empty((*packed.shape[:-1], packed.shape[-1] * 8), dtype=dtype, device=packed.device)
+    spattn_interface.unpack_mask(mask, packed)
+    return mask
+
+
+def packedmask_to_indexmask_cuda(packed: torch.Tensor, seq=None, stride=None):
+    """Packed mask [..., W/8] -> ascending lists int32 [..., stride] (default stride = W) + counts
+    [...]; entries >= `seq` are ignored; unused slots = stride."""
+    W = packed.shape[-1] * 8
+    stride = W if stride is None else stride
+    indices = torch.empty((*packed.shape[:-1], stride), dtype=torch.int32, device=packed.device)
+    num = torch.empty(packed.shape[:-1], dtype=torch.int32, device=packed.device)
+    spattn_interface.packedmask_to_indexmask(indices, num, packed.contiguous(), W if seq is None else seq, stride)
+    return indices, num
+
+
+def indexmask_to_packedmask_cuda(indices: torch.Tensor, num_indices: torch.Tensor, width: int) -> torch.Tensor:
+    """Lists int32 [..., stride] + counts -> packed mask uint8 [..., ceil(width / 32) * 4]."""
+    packed = torch.empty((*indices.shape[:-1], 4 * ((width + 31) // 32)), dtype=torch.uint8, device=indices.device)
+    spattn_interface.indexmask_to_packedmask(packed, indices.contiguous(), num_indices.contiguous())
+    return packed
 
 
 # ------------------------------------------------------------------------------------------------

@@ -37,11 +37,17 @@ def baseline_attn_maxq_denom(query, key, value, current_layer=None, ditrun=None,
     return out
 
 
-def _sparse(out, query, key, value, mask):
+def _sparse(out, query, key, value, mask, blocksz=128):
+    """One sparse step.  A 4-tuple (kb_indices, kb_counts, max_q, denom) carries the max_q / denom of
+    THESE query / key tensors and runs the non-renormalising block kernel; a pair of lists runs the
+    renormalising kernel of its granularity (key blocks for blocksz 64, key tokens otherwise), which is
+    what a mask cached from an earlier diffusion run needs."""
     q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
-    if len(mask) == 4:                                    # block mode: (kb_indices, kb_counts, max_q, denom)
+    if len(mask) == 4:
         spattn_interface.sp_attn_blocks_ml(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2], mask[3])
-    else:                                                 # token lists
+    elif blocksz == 64:
+        spattn_interface.sp_attn_blocks(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
+    else:
         spattn_interface.sp_attn(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
     return out
 
@@ -70,7 +76,7 @@ def compute_cache_and_attn_cuda(query, key, value, *args, **kwargs):
 def sparse_attn_from_cache_cuda(query, key, value, *args, **kwargs):
     """Sparse step from a cached mask (sparseattn_functionals.py:87-93)."""
     mask = kwargs["mask_cache"].get_mask_from_cache(kwargs.get("current_layer", 0))
-    return _sparse(_out(query), query, key, value, mask)
+    return _sparse(_out(query), query, key, value, mask[:2], kwargs.get("blocksz", 128))
 
 
 def cached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
@@ -79,9 +85,10 @@ def cached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
     mask_cache = kwargs["mask_cache"]
     if mask_cache.run_fullattn(ditrun):
         out, *mask = compute_cache_and_attn_cuda(query, key, value, thresh=kwargs["thresh"], blocksz=kwargs["blocksz"])
-        mask_cache.update_cache(current_layer, *mask)
+        mask_cache.update_cache(current_layer, *mask[:2])      # max_q / denom belong to this run's q, k only
         return out
-    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer))
+    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer)[:2],
+                   kwargs["blocksz"])
 
 
 def bitmaskcached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
@@ -97,4 +104,4 @@ def bitmaskcached_attn_cuda(query, key, value, current_layer, ditrun, *args, **k
                                                           blocksz=kwargs["blocksz"])
         mask_cache.update_cache(current_layer, mask, query.shape[2])
         return out
-    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer))
+    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer)[:2])

@@ -161,6 +161,33 @@ int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, 
                           const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_seq_len,
                           float scale, void* stream);
 
+/* ---- one-bit-per-entry masks (mask caches) ---------------------------------------------------
+ * Entry e of a row lives in byte e / 8, bit e % 8 (least significant bit first): the format of pack /
+ * unpack in python/spattn/mask_utils.py:421-440, which CompressedBitMaskCache (:87-98) stores.  A
+ * "row" is one (batch, head, query block); `width` entries per row, width % 8 == 0.  The same four
+ * calls serve token masks (width = mask_stride) and 64x64 block maps (width >= number of key blocks). */
+
+/* mask [rows, width] with elem_size 1 (bool / uint8) or 4 (int32), kept iff > 0 -> packed
+ * [rows, width / 8].  Replaces pack (python/spattn/mask_utils.py:421-430). */
+int fgattn_pack_mask(unsigned char* packed, const void* mask, int elem_size, long long rows, int width, void* stream);
+
+/* packed -> mask of 0 / 1 entries (elem_size 1 or 4).  Replaces unpack
+ * (python/spattn/mask_utils.py:433-440). */
+int fgattn_unpack_mask(void* mask, int elem_size, const unsigned char* packed, long long rows, int width, void* stream);
+
+/* packed mask rows -> ascending index lists [rows, list_stride] + counts [rows]: set bits at
+ * positions < n_valid, in ascending order; unused slots = sentinel.  Does in one kernel what
+ * CompressedBitMaskCache.get_mask_from_cache does as unpack + int conversion +
+ * booleanmask_to_indexmask (python/spattn/mask_utils.py:89-93), without materialising the int32 mask. */
+int fgattn_packedmask_to_indexmask(int* indices, int* num_indices, const unsigned char* packed, long long rows,
+                                   int width, int list_stride, int n_valid, int sentinel, void* stream);
+
+/* index lists -> packed mask rows: bit e is set iff e occurs among the first num_indices[r] entries
+ * of row r and e < width.  (The reference caches packed masks only from the int mask; this is the
+ * direct route from lists.) */
+int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, const int* num_indices, long long rows,
+                                   int list_stride, int width, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

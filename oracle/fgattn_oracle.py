@@ -128,6 +128,62 @@ def bitmask_to_indexmask(booleanmask) -> Tuple[torch.Tensor, torch.Tensor]:
     return idx, cnt
 
 
+def pack_mask(mask) -> np.ndarray:
+    """[..., W] map (bool, or numeric with > 0 = keep; W % 8 == 0) -> uint8 [..., W/8]: entry e of a
+    row sits in byte e // 8 at bit e % 8 (sum of bit * 2^(e % 8) over groups of eight).
+    Follows python/spattn/mask_utils.py:421-430."""
+    m = np.asarray(torch.as_tensor(mask).cpu().numpy())
+    m = m if m.dtype == np.bool_ else (m > 0)
+    assert m.shape[-1] % 8 == 0
+    g = m.reshape(*m.shape[:-1], m.shape[-1] // 8, 8).astype(np.uint16)
+    w = np.array([1, 2, 4, 8, 16, 32, 64, 128], dtype=np.uint16)
+    return (g * w).sum(axis=-1).astype(np.uint8)
+
+
+def unpack_mask(packed) -> np.ndarray:
+    """uint8 [..., W8] -> bool [..., 8 * W8]; inverse of pack_mask.
+    Follows python/spattn/mask_utils.py:433-440."""
+    p = np.asarray(torch.as_tensor(packed).cpu().numpy()).astype(np.uint8)
+    w = np.array([1, 2, 4, 8, 16, 32, 64, 128], dtype=np.uint8)
+    bits = (p[..., None] & w) != 0
+    return bits.reshape(*p.shape[:-1], p.shape[-1] * 8)
+
+
+def packedmask_to_indexmask(packed, n_valid: Optional[int] = None, stride: Optional[int] = None,
+                            sentinel: Optional[int] = None) -> Tuple[np.ndarray, np.ndarray]:
+    """What a compressed mask cache hands back (python/spattn/mask_utils.py:89-93: unpack, then the
+    row compaction of :152-167): ascending positions < n_valid of the set bits of every row, unused
+    slots = sentinel (default: the list stride, default: the row width), counts; both int32."""
+    bits = unpack_mask(packed)
+    W = bits.shape[-1]
+    n_valid = W if n_valid is None else min(n_valid, W)
+    stride = W if stride is None else stride
+    sentinel = stride if sentinel is None else sentinel
+    rows = bits.reshape(-1, W)
+    idx = np.full((rows.shape[0], stride), sentinel, dtype=np.int32)
+    cnt = np.zeros(rows.shape[0], dtype=np.int32)
+    for r in range(rows.shape[0]):
+        nz = np.flatnonzero(rows[r, :n_valid]).astype(np.int32)
+        cnt[r] = nz.size
+        idx[r, :min(nz.size, stride)] = nz[:stride]
+    return idx.reshape(*bits.shape[:-1], stride), cnt.reshape(bits.shape[:-1])
+
+
+def indexmask_to_packedmask(indices, num_indices, width: int) -> np.ndarray:
+    """Index lists + counts -> packed rows of ceil(width / 32) * 4 bytes: bit e set iff e < width is
+    among the first num_indices entries of the row (inverse of packedmask_to_indexmask)."""
+    idx = np.asarray(torch.as_tensor(indices).cpu().numpy())
+    cnt = np.asarray(torch.as_tensor(num_indices).cpu().numpy()).reshape(-1)
+    rows = idx.reshape(-1, idx.shape[-1])
+    Wp = 32 * ((width + 31) // 32)
+    bits = np.zeros((rows.shape[0], Wp), dtype=bool)
+    for r in range(rows.shape[0]):
+        e = rows[r, :min(int(cnt[r]), rows.shape[1])]
+        e = e[(e >= 0) & (e < width)]
+        bits[r, e] = True
+    return pack_mask(bits).reshape(*idx.shape[:-1], Wp // 8)
+
+
 def allindex_mask(B: int, H: int, max_stride: int, S: int, block: int):
     """Identity key lists: every key kept, in order.  Follows python/spattn/mask_utils.py:175-180
     and include/utils.cuh:73-93 (the all_index_mask operator)."""

@@ -96,6 +96,25 @@ def main(ref_root: str):
     idx, cnt = mu.boolean_to_index_mask_2d(bm)
     np.savez_compressed(HERE / "compaction_9x37.npz", mask=bm.numpy(), index=idx.numpy(), count=cnt.numpy())
 
+    # pack / unpack (mask_utils.py:421-440).  Both create their bit weights with device='cuda'; there
+    # is no GPU where the fixtures are made, so torch.tensor is wrapped to drop the device argument
+    # while the (unmodified) reference functions run.
+    real_tensor = torch.tensor
+    torch.tensor = lambda *a, **kw: real_tensor(*a, **{k_: v_ for k_, v_ in kw.items() if k_ != "device"})
+    try:
+        g = torch.Generator().manual_seed(11)
+        pm = torch.rand(2, 3, 5, 136, generator=g) < 0.2
+        pm[0, 0, 0] = False
+        pm[1, 2, 4] = True
+        packed = mu.pack(pm)
+        back = mu.unpack(packed)
+    finally:
+        torch.tensor = real_tensor
+    assert torch.equal(back, pm)
+    pidx, pcnt = mu.bitmask_to_indexmask(pm)                              # what the compressed cache returns
+    np.savez_compressed(HERE / "packed_2x3x5x136.npz", mask=pm.numpy(), packed=packed.numpy(),
+                        index=pidx.numpy().astype(np.int32), count=pcnt.numpy().astype(np.int32))
+
 
 if __name__ == "__main__":
     main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -86,3 +86,21 @@ def test_identity_list_equals_dense():
     kc = torch.full((1, 2, nkb), nkb, dtype=torch.int32)
     o2 = orc.sp_attn_blocks(g["q"], g["k"], g["v"], kb, kc)
     np.testing.assert_allclose(o2.numpy(), g["sdpa"], rtol=0, atol=2e-5)
+
+
+def test_packed_mask_fixture():
+    """pack / unpack of the reference (python/spattn/mask_utils.py:421-440) and the lists its
+    compressed cache rebuilds (:89-93)."""
+    z = np.load(GOLDEN / "packed_2x3x5x136.npz")
+    packed = orc.pack_mask(z["mask"])
+    assert packed.dtype == np.uint8 and np.array_equal(packed, z["packed"])
+    assert np.array_equal(orc.pack_mask(z["mask"].astype(np.int32) * 3), z["packed"])      # int mask, > 0 = keep
+    assert np.array_equal(orc.unpack_mask(z["packed"]), z["mask"])
+    idx, cnt = orc.packedmask_to_indexmask(z["packed"])
+    assert np.array_equal(idx, z["index"]) and np.array_equal(cnt, z["count"])
+    assert np.array_equal(orc.indexmask_to_packedmask(z["index"], z["count"], 136)[..., :17], z["packed"])
+    # n_valid cuts the tail, stride / sentinel are free
+    idx2, cnt2 = orc.packedmask_to_indexmask(z["packed"], n_valid=100, stride=140, sentinel=7)
+    ref = z["mask"].copy()
+    ref[..., 100:] = False
+    assert np.array_equal(cnt2, ref.sum(-1)) and (idx2[0, 0, 0] == 7).all()
