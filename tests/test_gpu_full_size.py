@@ -103,6 +103,52 @@ def test_c3_headline_full_size():
     assert d.max().item() <= 1e-2 and d.mean().item() <= 5e-4
 
 
+def test_c3_renormalising_full_size():
+    """The renormalising block kernel (lists replayed from a cache) on 8 heads of C3 with perturbed
+    queries: oracle on a row subset of one head; all blocks listed -> dense attention; rows of the
+    ragged C4 shape against the oracle."""
+    import dataclasses
+    from fgattn_tk_cuda_b200 import capi, synth
+    from oracle import fgattn_oracle as orc
+    w = synth.WORKLOADS["c3"]
+    q, k, v, idx, cnt, m, l, o_dense = _pipeline(w, heads=range(8))
+    B, H, S, D = q.shape
+    nqb = nkb = S // 64
+    q2 = (q.float() * 1.1 - 0.03).to(torch.bfloat16)          # the cached lists meet new queries
+    o = torch.full_like(q, float("nan"))
+    capi.sp_attn_blocks(o, q2, k, v, idx, cnt)
+    capi.check()
+    assert torch.isfinite(o.float()).all()
+    for h, r0 in ((3, 8192), (7, 16384 - 256)):
+        r1 = r0 + 256
+        ref = orc.sp_attn_blocks(q2[:, h:h + 1, r0:r1].cpu(), k[:, h:h + 1].cpu(), v[:, h:h + 1].cpu(),
+                                 idx[:, h:h + 1, r0 // 64:r1 // 64].cpu(), cnt[:, h:h + 1, r0 // 64:r1 // 64].cpu())
+        _close(o[:, h:h + 1, r0:r1], ref)
+    # same queries as the mask: renormalised output = masked output / kept mass, and the mass is ~1
+    o_same = torch.empty_like(q)
+    capi.sp_attn_blocks(o_same, q, k, v, idx, cnt)
+    capi.check()
+    assert (o_same.float() - o_dense.float()).abs().mean().item() < 2e-2
+    # every block listed -> dense attention
+    full_idx = torch.arange(nkb, dtype=torch.int32, device="cuda").expand(1, 2, nqb, nkb).contiguous()
+    full_cnt = torch.full((1, 2, nqb), nkb, dtype=torch.int32, device="cuda")
+    o2 = torch.empty_like(q[:, :2])
+    capi.sp_attn_blocks(o2, q[:, :2].contiguous(), k[:, :2].contiguous(), v[:, :2].contiguous(), full_idx, full_cnt)
+    capi.check()
+    d = (o2.float() - o_dense[:, :2].float()).abs()
+    assert d.max().item() <= 1e-2 and d.mean().item() <= 5e-4
+    # ragged shape (S = 12345, D = 64): last query blocks of one head
+    w4 = dataclasses.replace(synth.WORKLOADS["c4"], B=1, H=3)
+    q, k, v, idx, cnt, m, l, _ = _pipeline(w4)
+    o = torch.full_like(q, float("nan"))
+    capi.sp_attn_blocks(o, q, k, v, idx, cnt)
+    capi.check()
+    h, r0 = 1, 12032
+    ref = orc.sp_attn_blocks(q[:, h:h + 1, r0:].cpu(), k[:, h:h + 1].cpu(), v[:, h:h + 1].cpu(),
+                             idx[:, h:h + 1, r0 // 64:].cpu(), cnt[:, h:h + 1, r0 // 64:].cpu())
+    _close(o[:, h:h + 1, r0:], ref)
+
+
 def test_c4_ragged_full_length():
     """S=12345 (not a multiple of 64), D=64: the whole ragged pipeline on 6 of the 96 heads, one
     head against the oracle including the last, partial query / key blocks."""
