@@ -42,6 +42,8 @@ PROTOTYPES = {
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
     "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_topk_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "fgattn_topk_indices": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "fgattn_pack_mask": (_i, [_vp, _vp, _i, _ll, _i, _vp]),
     "fgattn_unpack_mask": (_i, [_vp, _i, _vp, _ll, _i, _vp]),
     "fgattn_packedmask_to_indexmask": (_i, [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp]),
@@ -254,3 +256,20 @@ def indexmask_to_packedmask(packed, indices, num_indices):
     with torch.cuda.device(packed.device):
         _call("fgattn_indexmask_to_packedmask", _ptr(packed), _ptr(indices), _ptr(num_indices),
               packed.numel() // packed.shape[-1], indices.shape[-1], W, _stream(packed))
+
+
+# ---- top-k selector ---------------------------------------------------------------------------------
+def topk_scratch_bytes(B, H, S, D, blocksz) -> int:
+    return int(lib().fgattn_topk_scratch_bytes(B, H, S, D, blocksz))
+
+
+def topk_indices(kv_indices, kv_num_indices, q, k, select_k, blocksz=128, kv_seq_len=None, scale=0.0, scratch=None):
+    """Per query block the select_k keys with the largest (block-mean query . key) score."""
+    _check_qkv(q, k)
+    B, H, S, D = q.shape
+    if scratch is None:
+        scratch = torch.empty(topk_scratch_bytes(B, H, S, D, blocksz), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _call("fgattn_topk_indices", _ptr(kv_indices), _ptr(kv_num_indices), kv_indices.shape[3], _ptr(q), _ptr(k),
+              int(select_k), B, H, S, D, int(blocksz), kv_seq_len or S, scale, _ptr(scratch),
+              scratch.numel() * scratch.element_size(), _stream(q))

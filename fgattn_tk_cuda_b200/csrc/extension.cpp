@@ -196,6 +196,21 @@ void indexmask_to_packedmask(torch::Tensor packed, torch::Tensor indices, torch:
                "indexmask_to_packedmask");
 }
 
+// ---- top-k selector (addition) ------------------------------------------------------------------
+void topk_indices(torch::Tensor kv_indices, torch::Tensor kv_num_indices, torch::Tensor q, torch::Tensor k,
+                  int64_t select_k, int64_t blocksz) {
+  check_bf16_4d(q, "q"); check_bf16_4d(k, "k");
+  check_dtype(kv_indices, at::kInt, "kv_indices"); check_dtype(kv_num_indices, at::kInt, "kv_num_indices");
+  TORCH_CHECK(kv_indices.dim() == 4, "kv_indices must be [B, H, blocks, stride]");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t bytes = int64_t(fgattn_topk_scratch_bytes(q.size(0), q.size(1), q.size(2), q.size(3), int(blocksz)));
+  torch::Tensor scratch = torch::empty({bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
+  check_status(fgattn_topk_indices(kv_indices.data_ptr<int>(), kv_num_indices.data_ptr<int>(), int(kv_indices.size(3)),
+                                   q.data_ptr(), k.data_ptr(), int(select_k), q.size(0), q.size(1), q.size(2),
+                                   q.size(3), int(blocksz), k.size(2), 0.f, scratch.data_ptr(), size_t(bytes),
+                                   stream_of(q)), "topk_indices");
+}
+
 int64_t block_scratch_bytes(int64_t batch, int64_t heads, int64_t seq, int64_t kv_seq_len) {
   return int64_t(fgattn_block_scratch_bytes(int(batch), int(heads), int(seq), int(kv_seq_len)));
 }
@@ -213,6 +228,7 @@ void meta_bil(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, c10::o
 void meta2(torch::Tensor, torch::Tensor) {}
 void meta3(torch::Tensor, torch::Tensor, torch::Tensor) {}
 void meta_p2i(torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t) {}
+void meta_topk(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t) {}
 
 }  // namespace
 
@@ -234,6 +250,8 @@ TORCH_LIBRARY_FRAGMENT(cuda_attn, m) {
   m.def("unpack_mask(Tensor (mask!) mask, Tensor packed) -> ()");
   m.def("packedmask_to_indexmask(Tensor (indices!) indices, Tensor (num_indices!) num_indices, Tensor packed, int n_valid, int sentinel) -> ()");
   m.def("indexmask_to_packedmask(Tensor (packed!) packed, Tensor indices, Tensor num_indices) -> ()");
+  // top-k selector
+  m.def("topk_indices(Tensor (kv_indices!) kv_indices, Tensor (kv_num_indices!) kv_num_indices, Tensor q, Tensor k, int select_k, int blocksz) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(cuda_attn, Meta, m) {
@@ -251,6 +269,7 @@ TORCH_LIBRARY_IMPL(cuda_attn, Meta, m) {
   m.impl("unpack_mask", meta2);
   m.impl("packedmask_to_indexmask", meta_p2i);
   m.impl("indexmask_to_packedmask", meta3);
+  m.impl("topk_indices", meta_topk);
 }
 
 TORCH_LIBRARY_IMPL(cuda_attn, CUDA, m) {
@@ -268,6 +287,7 @@ TORCH_LIBRARY_IMPL(cuda_attn, CUDA, m) {
   m.impl("unpack_mask", unpack_mask);
   m.impl("packedmask_to_indexmask", packedmask_to_indexmask);
   m.impl("indexmask_to_packedmask", indexmask_to_packedmask);
+  m.impl("topk_indices", topk_indices);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -286,4 +306,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("unpack_mask", &unpack_mask, "one bit per entry -> mask");
   m.def("packedmask_to_indexmask", &packedmask_to_indexmask, "packed mask -> ascending index lists");
   m.def("indexmask_to_packedmask", &indexmask_to_packedmask, "index lists -> packed mask");
+  m.def("topk_indices", &topk_indices, "top-k keys per query block");
 }

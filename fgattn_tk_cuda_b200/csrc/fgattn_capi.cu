@@ -13,6 +13,7 @@
 #include "sparse_ml_persistent.cuh"
 #include "sparse_token_attn.cuh"
 #include "tensor_map.h"
+#include "topk_select.cuh"
 
 namespace {
 
@@ -591,6 +592,76 @@ int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, 
                           float scale, void* stream) {
   return launch_sparse<true>(o, q, k, v, kb_indices, kb_counts, list_stride, nullptr, nullptr, batch, heads, seq, D,
                              kv_seq_len, scale, static_cast<cudaStream_t>(stream));
+}
+
+// ---- top-k selector ------------------------------------------------------------------------------
+namespace {
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+}  // namespace
+
+size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz) {
+  if (batch <= 0 || heads <= 0 || seq <= 0 || D <= 0 || blocksz <= 0) return 0;
+  const size_t bh = size_t(batch) * heads, nblk = size_t((seq + blocksz - 1) / blocksz);
+  const size_t s_stride = size_t((seq + 127) / 128) * 128;
+  return 2 * align256(bh * nblk * D * 2) + bh * nblk * s_stride * sizeof(float);
+}
+
+int fgattn_topk_indices(int* kv_indices, int* kv_num_indices, int list_stride, const void* q, const void* k,
+                        int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_seq_len, float scale,
+                        void* scratch, size_t scratch_bytes, void* stream) {
+  int r = check_qk(q, k, batch, heads, seq, D, kv_seq_len);
+  if (r) return r;
+  if (!kv_indices || !kv_num_indices || !scratch || blocksz < 1) return FGATTN_INVALID_ARGUMENT;
+  if (select_k < 1 || select_k > kv_seq_len || list_stride < select_k) return FGATTN_INVALID_ARGUMENT;
+  if (select_k > 8192) return FGATTN_UNSUPPORTED;          // the selected pairs are sorted in shared memory
+  if (!aligned16(scratch)) return FGATTN_MISALIGNED;
+  if (scratch_bytes < fgattn_topk_scratch_bytes(batch, heads, seq, D, blocksz)) return FGATTN_SCRATCH_TOO_SMALL;
+  const int bh = batch * heads, nblk = (seq + blocksz - 1) / blocksz, s_stride = ((seq + 127) / 128) * 128;
+  if ((long long)bh * nblk > 2147483647LL || nblk > 65535 * 128) return FGATTN_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(scratch);
+  const size_t mean_bytes = align256(size_t(bh) * nblk * D * 2);
+  __nv_bfloat16* qm_hi = reinterpret_cast<__nv_bfloat16*>(base);
+  __nv_bfloat16* qm_lo = reinterpret_cast<__nv_bfloat16*>(base + mean_bytes);
+  float* scores = reinterpret_cast<float*>(base + 2 * mean_bytes);
+  const float sc = (scale > 0.f) ? scale : 1.0f / sqrtf(float(D));
+  fg::TopkScoreParams p;
+  p.scores = scores;
+  p.n_blocks = nblk;
+  p.kv_len = kv_seq_len;
+  p.s_stride = s_stride;
+  r = get_err_word(&p.err);
+  if (r) return r;
+  CUtensorMap m_hi, m_lo, mk;
+  if (fg::make_qkv_map(&m_hi, qm_hi, bh, nblk, D, 128) || fg::make_qkv_map(&m_lo, qm_lo, bh, nblk, D, 128) ||
+      fg::make_qkv_map(&mk, k, bh, seq, D, 128))
+    return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
+  const dim3 g_mean(nblk, bh), g_sc(s_stride / 128, (nblk + 127) / 128, bh);
+  if (D == 128) {
+    fg::qblock_mean_kernel<128><<<g_mean, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(q), qm_hi, qm_lo, seq, nblk,
+                                                       blocksz, sc);
+    auto kern = fg::topk_scores_kernel<128>;
+    r = set_smem(kern, fg::TopkScoreCfg<128>::kSmemBytes);
+    if (r) return r;
+    kern<<<g_sc, fg::TopkScoreCfg<128>::kThreads, fg::TopkScoreCfg<128>::kSmemBytes, st>>>(m_hi, m_lo, mk, p);
+  } else {
+    fg::qblock_mean_kernel<64><<<g_mean, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(q), qm_hi, qm_lo, seq, nblk,
+                                                      blocksz, sc);
+    auto kern = fg::topk_scores_kernel<64>;
+    r = set_smem(kern, fg::TopkScoreCfg<64>::kSmemBytes);
+    if (r) return r;
+    kern<<<g_sc, fg::TopkScoreCfg<64>::kThreads, fg::TopkScoreCfg<64>::kSmemBytes, st>>>(m_hi, m_lo, mk, p);
+  }
+  FG_CUDA(cudaGetLastError());
+  int k_pow2 = 2;
+  while (k_pow2 < select_k) k_pow2 <<= 1;
+  const int smem_sel = k_pow2 * 8;
+  r = set_smem(fg::topk_select_kernel, std::max(smem_sel, 1024));
+  if (r) return r;
+  fg::topk_select_kernel<<<unsigned(bh * nblk), fg::kSelThreads, smem_sel, st>>>(
+      scores, s_stride, kv_seq_len, select_k, k_pow2, kv_indices, kv_num_indices, list_stride);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
 }
 
 }  // extern "C"

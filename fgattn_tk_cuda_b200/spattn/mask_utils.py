@@ -234,3 +234,27 @@ def qk_indexmask_cuda(q, k, thresh, blocksz=128):
     assert blocksz == 128
     max_q, denom = _maxq_denom(q, k)
     return qk_indexmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz)
+
+
+# ------------------------------------------------------------------------------------------------
+# alternative selectors (python/spattn/mask_utils.py:385-417)
+# ------------------------------------------------------------------------------------------------
+def qk_lshmask_indices(query, key, thresh, blocksz=128):
+    """Not implemented in the reference either (python/spattn/mask_utils.py:385-386)."""
+    raise NotImplementedError
+
+
+def qk_topkmask_indices(q, k, select_k, B=None, H=None, S=None, D=None, BLOCKSZ=128, blocksz=None, max_stride=None):
+    """Per block of BLOCKSZ query rows the select_k keys with the largest (block-mean query . key)/sqrt(D),
+    descending (python/spattn/mask_utils.py:389-417; B, H, S, D are taken from q when omitted).  The
+    list stride is select_k rounded up to a multiple of 128 (unused slots = stride), the form the
+    sp_attn operator takes."""
+    BLOCKSZ = BLOCKSZ if blocksz is None else blocksz
+    Bq, Hq, Sq, _ = q.shape
+    nblk = (Sq + BLOCKSZ - 1) // BLOCKSZ
+    stride = _pad128(select_k) if max_stride is None else max_stride
+    kv_indices = torch.empty((Bq, Hq, nblk, stride), dtype=torch.int32, device=q.device)
+    kv_num_indices = torch.empty((Bq, Hq, nblk), dtype=torch.int32, device=q.device)
+    spattn_interface.topk_indices(kv_indices, kv_num_indices, q.contiguous(), k.contiguous(), int(select_k),
+                                  int(BLOCKSZ))
+    return kv_indices, kv_num_indices

@@ -59,6 +59,19 @@ def attn_computed_with_sparse_mask_cuda(query, key, value, *args, **kwargs):
     return _sparse(_out(query), query, key, value, mask)
 
 
+def attn_topkmask_cuda(query, key, value, current_layer=None, ditrun=None, *args, **kwargs):
+    """Top-k key selection per 128-row query block, then the token-list sparse kernel
+    (sparseattn_functionals.py:39-48)."""
+    select_k = kwargs.get("select_k") or query.shape[2]
+    mask = mask_utils.qk_topkmask_indices(query, key, select_k, blocksz=kwargs.get("blocksz", 128))
+    return _sparse(_out(query), query, key, value, mask)
+
+
+def attn_lshmask_cuda(query, key, value, current_layer=None, ditrun=None, *args, **kwargs):
+    """The LSH selector is a stub in the reference (mask_utils.py:385-386); it stays one."""
+    raise NotImplementedError
+
+
 def compute_cache_and_attn_cuda(query, key, value, *args, **kwargs):
     """Dense attention + mask in one go (sparseattn_functionals.py:74-84).  Returns
     (out, kv_indices, kv_num_indices) and, in block mode, additionally (max_q, denom)."""

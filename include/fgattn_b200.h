@@ -188,6 +188,22 @@ int fgattn_packedmask_to_indexmask(int* indices, int* num_indices, const unsigne
 int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, const int* num_indices, long long rows,
                                    int list_stride, int width, void* stream);
 
+/* ---- top-k selector ------------------------------------------------------------------------- */
+
+/* Bytes of scratch fgattn_topk_indices needs (block means as two bf16 tensors + the fp32 score rows). */
+size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz);
+
+/* Alternative list producer: for every block of `blocksz` query rows (the last block may be shorter)
+ * score(key) = mean of the block's query rows . key * scale, and the select_k keys < kv_seq_len with the
+ * largest score are listed in kv_indices int32 [B,H,ceil(S/blocksz),list_stride] in descending score
+ * order (equal scores: smaller key index first); unused slots = list_stride; kv_num_indices = select_k.
+ * The lists feed fgattn_sp_attn.  Scores are computed in fp32 from the bf16 inputs (the reference
+ * rounds block means and scores to bf16, which makes its order among near-equal scores arbitrary).
+ * select_k <= 8192.  Replaces qk_topkmask_indices (python/spattn/mask_utils.py:389-417). */
+int fgattn_topk_indices(int* kv_indices, int* kv_num_indices, int list_stride, const void* q, const void* k,
+                        int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_seq_len, float scale,
+                        void* scratch, size_t scratch_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

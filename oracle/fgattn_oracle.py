@@ -184,6 +184,29 @@ def indexmask_to_packedmask(indices, num_indices, width: int) -> np.ndarray:
     return pack_mask(bits).reshape(*idx.shape[:-1], Wp // 8)
 
 
+def topk_scores(q, k, blocksz: int = 128, kv_seq_len: Optional[int] = None,
+                scale: Optional[float] = None) -> torch.Tensor:
+    """[B, H, ceil(S/blocksz), n_kv] fp32: mean of each block of query rows (the last block may be
+    shorter), times scale, dotted with every key.  Follows python/spattn/mask_utils.py:390-411."""
+    q, k = _f32(q), _f32(k)
+    B, H, S, D = q.shape
+    n_kv = k.shape[2] if kv_seq_len is None else kv_seq_len
+    scale = (1.0 / math.sqrt(D)) if scale is None else scale
+    nblk = (S + blocksz - 1) // blocksz
+    qmean = torch.stack([q[:, :, i * blocksz:min(S, (i + 1) * blocksz)].mean(dim=2) for i in range(nblk)], dim=2)
+    return torch.einsum("bhmd,bhnd->bhmn", qmean * scale, k[:, :, :n_kv])
+
+
+def topk_indices(q, k, select_k: int, blocksz: int = 128, kv_seq_len: Optional[int] = None,
+                 scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The select_k keys with the largest topk_scores per query block, descending (equal scores:
+    smaller index first), int32, and counts = select_k.  Follows python/spattn/mask_utils.py:412-417."""
+    sc = topk_scores(q, k, blocksz, kv_seq_len, scale)
+    order = torch.sort(sc, dim=-1, descending=True, stable=True).indices[..., :select_k]
+    cnt = torch.full(sc.shape[:3], select_k, dtype=torch.int32)
+    return order.to(torch.int32), cnt
+
+
 def allindex_mask(B: int, H: int, max_stride: int, S: int, block: int):
     """Identity key lists: every key kept, in order.  Follows python/spattn/mask_utils.py:175-180
     and include/utils.cuh:73-93 (the all_index_mask operator)."""

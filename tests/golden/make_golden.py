@@ -115,6 +115,19 @@ def main(ref_root: str):
     np.savez_compressed(HERE / "packed_2x3x5x136.npz", mask=pm.numpy(), packed=packed.numpy(),
                         index=pidx.numpy().astype(np.int32), count=pcnt.numpy().astype(np.int32))
 
+    # top-k selector (mask_utils.py:389-417) on fp32 copies of bf16-representable inputs; ragged last
+    # query block (300 = 2 * 128 + 44).  The function prints its result; that output is discarded.
+    import contextlib, io
+    g = torch.Generator().manual_seed(21)
+    B, H, S, D, K = 1, 2, 300, 64, 40
+    tq = bf16_round(torch.randn(B, H, S, D, generator=g))
+    tk = bf16_round(torch.randn(B, H, S, D, generator=g))
+    with contextlib.redirect_stdout(io.StringIO()):
+        tidx, tcnt = mu.qk_topkmask_indices(tq, tk, K, B, H, S, D, 128)
+    np.savez_compressed(HERE / "topk_s300_d64_k40.npz", q_bf16=tq.to(torch.bfloat16).view(torch.int16).numpy(),
+                        k_bf16=tk.to(torch.bfloat16).view(torch.int16).numpy(), index=tidx.numpy().astype(np.int32),
+                        count=tcnt.numpy().astype(np.int32), select_k=np.int64(K), blocksz=np.int64(128))
+
 
 if __name__ == "__main__":
     main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -104,3 +104,13 @@ def test_packed_mask_fixture():
     ref = z["mask"].copy()
     ref[..., 100:] = False
     assert np.array_equal(cnt2, ref.sum(-1)) and (idx2[0, 0, 0] == 7).all()
+
+
+def test_topk_fixture():
+    """qk_topkmask_indices of the reference (python/spattn/mask_utils.py:389-417) on a ragged shape."""
+    z = np.load(GOLDEN / "topk_s300_d64_k40.npz")
+    q = torch.from_numpy(z["q_bf16"]).view(torch.bfloat16).float()
+    k = torch.from_numpy(z["k_bf16"]).view(torch.bfloat16).float()
+    idx, cnt = orc.topk_indices(q, k, int(z["select_k"]), int(z["blocksz"]))
+    assert np.array_equal(cnt.numpy(), z["count"])
+    assert np.array_equal(idx.numpy(), z["index"])
