@@ -246,6 +246,13 @@ def main():
     ms_p2i = ev_time(lambda: capi.packedmask_to_indexmask(tidx, tcnt, tpacked, S), 10, 3)
     ms_m2i = ev_time(lambda: capi.booleanmask_to_indexmask(tidx, tcnt, tmask, S), 10, 3)
     del tmask, tidx
+    # top-k selector at the reference granularity: 128-row query blocks, 10 % of the keys
+    sel_k = max(1, S // 10)
+    kstride = 128 * ((sel_k + 127) // 128)
+    kidx = torch.empty(B, H, (S + 127) // 128, kstride, dtype=torch.int32, device=dev)
+    tk_scratch = torch.empty(capi.topk_scratch_bytes(B, H, S, D, 128), dtype=torch.uint8, device=dev)
+    ms_topk = ev_time(lambda: capi.topk_indices(kidx, tcnt, q, k, sel_k, blocksz=128, scratch=tk_scratch), 5, 2)
+    del kidx, tk_scratch
 
     step = lambda: torch.ops.cuda_attn.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
 
@@ -327,6 +334,7 @@ def main():
                 "packedmask_to_indexmask_ms": ms_p2i, "packedmask_to_indexmask_gbs": pack_bytes / ms_p2i / 1e6,
                 "packedmask_to_indexmask_frac_of_hbm_peak": pack_bytes / ms_p2i / 1e6 / peaks["hbm_gbs"],
                 "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
+                "topk_indices_ms": ms_topk, "topk_select_k": sel_k,
                 "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
                 "sparse_ms": ms_step, "sparse_speedup_over_full": ms_full / ms_step,
                 "ideal_speedup_1_over_density": 1.0 / density,
