@@ -50,6 +50,20 @@ def test_argument_validation_needs_no_device():
     assert lib.fgattn_maxq_denom(null, null, buf, buf, 1, 1, 64, 64, 64, 0.0, null) == 1
     assert lib.fgattn_booleanmask_to_indexmask(buf, buf, buf, 1, 1, 64, 0, 128, null) == 1
     assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 0.0, buf, 64, null) == 1
+    # one-bit-per-entry masks
+    assert lib.fgattn_pack_mask(null, buf, 4, 8, 64, null) == 1                             # null output
+    assert lib.fgattn_pack_mask(buf, buf, 2, 8, 64, null) == 2                              # element size
+    assert lib.fgattn_pack_mask(buf, buf, 4, 8, 60, null) == 1                              # width % 8
+    assert lib.fgattn_pack_mask(buf, ctypes.c_void_p(0x1004), 4, 8, 64, null) == 3          # int32 mask, 16-byte rule
+    assert lib.fgattn_unpack_mask(buf, 1, null, 8, 64, null) == 1
+    assert lib.fgattn_packedmask_to_indexmask(buf, buf, buf, 8, 64, 0, 64, 64, null) == 1   # list stride
+    assert lib.fgattn_indexmask_to_packedmask(buf, buf, buf, 8, 64, 8 * 64 * 1024, null) == 2   # row too wide
+    # top-k selector
+    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 0, 1, 1, 256, 64, 128, 256, 0.0, buf, 1 << 30, null) == 1
+    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 129, 1, 1, 256, 64, 128, 256, 0.0, buf, 1 << 30, null) == 1
+    assert lib.fgattn_topk_indices(buf, buf, 16384, buf, buf, 9000, 1, 1, 16384, 64, 128, 16384, 0.0, buf, 1 << 40, null) == 2
+    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 64, 1, 1, 256, 64, 128, 256, 0.0, buf, 16, null) == 7
+    assert capi.topk_scratch_bytes(1, 12, 32760, 128, 128) == 2 * 12 * 256 * 128 * 2 + 12 * 256 * 32768 * 4
 
 
 def test_python_layer_refuses_cpu_tensors():
