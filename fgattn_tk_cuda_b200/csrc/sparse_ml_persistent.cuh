@@ -7,15 +7,21 @@
 // longest-list-first.
 //
 // Because the probabilities are p = 2^(s*c - (m*c + log2 l)) with m, l given, no row reduction is
-// needed and the two softmax warpgroups split the COLUMNS of a score tile (keys 0-63 / 64-127, i.e.
-// one listed key block each).
+// needed, so the softmax work of a step can be cut by columns: four softmax warpgroups form two
+// pairs that take the steps alternately (pair = step parity), and inside a pair each warpgroup owns
+// one of the step's two 64-key blocks, one query row per thread.  While one pair is in the
+// exponential-bound part of its step the other pair is in the wait / load / store / signal part of
+// the next one.
 //
-// Tensor memory (512 columns): scores S[2] (2 x 128), probabilities P[2] (2 x 64, packed bf16),
-// output accumulator O (128).  Scores and probabilities have their own double buffers, so the
-// three pipelines only meet through full/empty barriers two steps apart:
-//   Q K^T issuer           : S[s&1] = Q K_s^T           needs K_s and S[s&1] drained by the softmax
-//   softmax warpgroups     : P[s&1] = 2^(S[s&1]*c - t)  needs S[s&1]; P[s&1] consumed by P*V of s-2
-//   P V issuer             : O += P[s&1] V_s            needs both halves of P[s&1] and V_s
+// Tensor memory (512 columns): three 128-column score buffers S[3] and the output accumulator O
+// (128).  A warpgroup writes its packed bf16 probabilities over the first half of its OWN score
+// columns, so there are no separate probability buffers and nothing to wait for before the store;
+// a buffer is handed back to the Q K^T issuer by the commit of the P*V product that consumed it:
+//   Q K^T issuer           : S[s%3] = Q K_s^T           needs K_s and the P*V product of step s-3
+//   softmax pair (s&1)     : P (in S[s%3]) = 2^(S*c - t) needs S[s%3]
+//   P V issuer             : O += P V_s                  needs both key blocks of P and V_s
+// Barriers that a role waits on only every other step (score-full, probability-full) exist once per
+// (buffer, pair), i.e. per step mod 6, because a parity wait must see every phase of its barrier.
 // Service warps after the softmax warps: TMA producer of Q and the K ring, Q K^T issuer, scheduler
 // (queue + union lists, up to three items ahead), P V issuer, TMA producer of the V ring.
 #pragma once
@@ -25,9 +31,6 @@
 
 #ifndef FG_POLY_OF8
 #define FG_POLY_OF8 0
-#endif
-#ifndef FG_ML_SMWGS
-#define FG_ML_SMWGS 4          // softmax warpgroups per CTA (2 or 4)
 #endif
 
 namespace fg {
@@ -55,15 +58,14 @@ struct SparseMLCfg {
   static constexpr int kVStages = (D == 128) ? 2 : 4;
   static constexpr int kListBufs = 4;
   // warp roles: [0, kSmWarps) softmax, then K producer, QK issuer, scheduler, PV issuer, V producer
-  static constexpr int kSmWGs = FG_ML_SMWGS;
+  static constexpr int kSmWGs = 4;                        // two pairs of softmax warpgroups
   static constexpr int kSmWarps = 4 * kSmWGs;
   static constexpr int kWarpProdK = kSmWarps, kWarpQK = kSmWarps + 1, kWarpSched = kSmWarps + 2,
                        kWarpPV = kSmWarps + 3, kWarpProdV = kSmWarps + 4;
   static constexpr int kThreads = 32 * (kSmWarps + 8);
-  static constexpr int kColsPerWG = 128 / kSmWGs;         // score columns per softmax warpgroup and step
   // registers: the CTA owns (launch registers x threads); service warps shrink, softmax warps grow
-  static constexpr int kRegsService = (kSmWGs == 2) ? 48 : 40;
-  static constexpr int kRegsSoftmax = (kSmWGs == 2) ? 208 : 96;
+  static constexpr int kRegsService = 40;
+  static constexpr int kRegsSoftmax = 96;
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = 2 * kTileBytes;
   static constexpr int kOffV = kOffK + kKStages * kTileBytes;
@@ -84,13 +86,13 @@ enum : int {
   PB_K_EMPTY = 16,     // +stage
   PB_V_FULL = 20,      // +stage (<=4)
   PB_V_EMPTY = 24,     // +stage
-  PB_S_FULL = 28,      // +sbuf (2)
-  PB_S_EMPTY = 30,     // +sbuf (2)
-  PB_P_EMPTY = 32,     // +pbuf (2)
-  PB_O_FULL = 34,
-  PB_O_EMPTY = 35,
-  PB_P_FULL = 36,      // +pbuf*kSmWGs + warpgroup (<= 8)
-  PB_COUNT = 44
+  PB_S_FULL = 28,      // +(step % 6) (6): a barrier per (score buffer, owning pair), so that every waiter of a
+                       // barrier waits for each of its phases (a parity wait cannot skip phases)
+  PB_S_EMPTY = 34,     // +score buffer (3): the P*V product that read the buffer's probabilities is done
+  PB_O_FULL = 37,
+  PB_O_EMPTY = 38,
+  PB_P_FULL = 40,      // +(step % 6) * 2 + key block of the step (12)
+  PB_COUNT = 52
 };
 
 struct ItemInfo {
@@ -156,7 +158,8 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int words = (p.nkb + 31) / 32;
-  constexpr uint32_t kColS = 0, kColP = 256, kColO = 384;
+  constexpr uint32_t kColS = 0, kColO = 384;           // three 128-column score buffers, then the accumulator
+  constexpr int kSB = 3;
 
   if (tid == 0) {
     ab->flag = 0;
@@ -167,10 +170,11 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(PB_Q_FULL + b), 1);
       mbar_init(bar(PB_Q_EMPTY + b), 1);
-      mbar_init(bar(PB_S_FULL + b), 1);
-      mbar_init(bar(PB_S_EMPTY + b), Cfg::kSmWarps);     // one arrival per softmax warp
-      for (int g = 0; g < Cfg::kSmWGs; ++g) mbar_init(bar(PB_P_FULL + b * Cfg::kSmWGs + g), 4);
-      mbar_init(bar(PB_P_EMPTY + b), 1);
+    }
+    for (int b = 0; b < kSB; ++b) mbar_init(bar(PB_S_EMPTY + b), 1);
+    for (int i = 0; i < 6; ++i) {
+      mbar_init(bar(PB_S_FULL + i), 1);
+      for (int kb = 0; kb < 2; ++kb) mbar_init(bar(PB_P_FULL + i * 2 + kb), 4);
     }
     for (int s = 0; s < 4; ++s) {
       mbar_init(bar(PB_K_FULL + s), 1);
@@ -363,9 +367,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         FG_TW(w_misc, ok = mbar_wait_warp(bar(PB_Q_FULL + qb), (u >> 1) & 1, ab, p.err, 1202));
         const uint32_t qa = sbase + Cfg::kOffQ + qb * Cfg::kTileBytes;
         for (int j = 0; j < n && ok; ++j, ++s) {
-          const int ks = s % Cfg::kKStages, sbuf = s & 1;
+          const int ks = s % Cfg::kKStages, sbuf = s % kSB;
           FG_TW(w_k, ok = mbar_wait_warp(bar(PB_K_FULL + ks), (s / Cfg::kKStages) & 1, ab, p.err, 1203));
-          if (ok && s >= 2) FG_TW(w_se, ok = mbar_wait_warp(bar(PB_S_EMPTY + sbuf), ((s >> 1) - 1) & 1, ab, p.err, 1204));
+          if (ok && s >= kSB) FG_TW(w_se, ok = mbar_wait_warp(bar(PB_S_EMPTY + sbuf), ((s / kSB) - 1) & 1, ab, p.err, 1204));
           if (!ok) break;
           tc_fence_after();
           const uint32_t ka = sbase + Cfg::kOffK + ks * Cfg::kTileBytes;
@@ -377,7 +381,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
                             umma_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0);
             }
           }
-          umma_commit_elect(bar(PB_S_FULL + sbuf));
+          umma_commit_elect(bar(PB_S_FULL + s % 6));
           umma_commit_elect(bar(PB_K_EMPTY + ks));
           if (j == n - 1) umma_commit_elect(bar(PB_Q_EMPTY + qb));
         }
@@ -407,26 +411,26 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         // the accumulator is single-buffered: the previous item's rows must have been read out
         if (u >= 1) FG_TW(w_o, ok = mbar_wait_warp(bar(PB_O_EMPTY), (u - 1) & 1, ab, p.err, 1302));
         for (int j = 0; j < n && ok; ++j, ++s) {
-          const int vs = s % Cfg::kVStages, pbuf = s & 1;
+          const int vs = s % Cfg::kVStages, pbuf = s % kSB;
           FG_TW(w_v, ok = mbar_wait_warp(bar(PB_V_FULL + vs), (s / Cfg::kVStages) & 1, ab, p.err, 1303));
           const uint32_t va = sbase + Cfg::kOffV + vs * Cfg::kTileBytes;
-          constexpr int kStepsPerWG = Cfg::kColsPerWG / 16;     // UMMA k-steps (16 keys) per softmax warpgroup
-          for (int g = 0; g < Cfg::kSmWGs && ok; ++g) {
-            FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + pbuf * Cfg::kSmWGs + g), (s >> 1) & 1, ab, p.err, 1304));
+          // the step's two key blocks come from the two warpgroups of the pair that owns the step
+          for (int kb = 0; kb < 2 && ok; ++kb) {
+            FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + (s % 6) * 2 + kb), (s / 6) & 1, ab, p.err, 1304));
             if (!ok) break;
             tc_fence_after();
             if (!(p.debug & 2)) {
 #pragma unroll
-              for (int kk = 0; kk < kStepsPerWG; ++kk) {
-                const int ks = g * kStepsPerWG + kk;
-                umma_ts_elect(tmem + kColO, tmem + kColP + pbuf * 64 + ks * 8,
+              for (int kk = 0; kk < 4; ++kk) {
+                const int ks = kb * 4 + kk;                   // 16-key step inside the 128-key tile
+                umma_ts_elect(tmem + kColO, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8,
                               umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
               }
             }
           }
           if (!ok) break;
           umma_commit_elect(bar(PB_V_EMPTY + vs));
-          umma_commit_elect(bar(PB_P_EMPTY + pbuf));
+          umma_commit_elect(bar(PB_S_EMPTY + pbuf));       // scores and probabilities of this buffer are consumed
           if (j == n - 1) umma_commit_elect(bar(PB_O_FULL));
         }
         ++u;
@@ -438,19 +442,17 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     }
   } else if (warp < Cfg::kSmWarps) {
     // ------------------------------------------------------------------ softmax warpgroups
-    // Every softmax warpgroup works on every step: warpgroup g turns kColsPerWG columns of the
-    // 128-key score tile (keys g*kColsPerWG ...) into probabilities, one query row per thread.  More
-    // warpgroups = narrower slices per warp and more warps per sub-partition to hide the
-    // wait / load / store / signal latencies of a step behind other warps' exponentials.
+    // Two pairs of warpgroups take the steps alternately; a warpgroup turns the 64 score columns of
+    // one key block into probabilities, one query row per thread, in two 32-column halves.
     reg_alloc<Cfg::kRegsSoftmax>();
     const int wg = warp >> 2, wq = warp & 3, half = wq >> 1;
     const int row_in_tile = wq * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
     const float c = p.scale_log2;
     constexpr int kOCols = D / Cfg::kSmWGs;              // output columns stored by this warpgroup
-    constexpr int kCols = Cfg::kColsPerWG;
-    const int kb_sel = wg / (Cfg::kSmWGs / 2);           // which of the step's two key blocks
-    const int col_in_kb = (wg % (Cfg::kSmWGs / 2)) * kCols;
+    static_assert(Cfg::kSmWGs == 4, "two pairs of softmax warpgroups");
+    const int own = wg >> 1;                             // this warpgroup owns the steps with (s & 1) == own
+    const int kb_sel = wg & 1;                           // which of an owned step's two key blocks
     int s = 0, u = 0;
     bool ok = true;
     long long w_s = 0, w_list = 0, w_epi = 0, w_pe = 0, t_math = 0, t_prol = 0, t_epiw = 0, t_ld = 0, t_st = 0,
@@ -517,48 +519,48 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         t_prol += FG_CLK() - tp0;
         const uint32_t* list = lists + lb * p.list_cap;
         for (int j = 0; j < n; ++j, ++s) {
+          if ((s & 1) != own) {
+            // the other pair's step; an item's first step is a good moment for the pending rows
+            if (j == 0 && pe) {
+              epilogue();
+              if (!ok) break;
+            }
+            continue;
+          }
           const uint32_t e = list[2 * j + kb_sel];
           const int valid_kb = ((e >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e) * 64) : 0;
-          const int valid = max(0, min(kCols, valid_kb - col_in_kb));
-          const int sbuf = s & 1;
-          FG_TW(w_s, ok = mbar_wait(bar(PB_S_FULL + sbuf), (s >> 1) & 1, ab, p.err, 1403));
+          const int sbuf = s % kSB;
+          FG_TW(w_s, ok = mbar_wait(bar(PB_S_FULL + s % 6), (s / 6) & 1, ab, p.err, 1403));
           if (!ok) break;
           tc_fence_after();
           long long tm0 = FG_CLK();
-          uint32_t pk[kCols / 2];
-          if (valid > 0 && !(p.debug & 4)) {             // warp-uniform
-            uint32_t r[kCols];
-            const uint32_t a = lane_base + kColS + sbuf * 128 + wg * kCols;
+          // 64 score columns (one key block) in two halves; the probabilities go over the first half
+          // of this warpgroup's own score columns, which nobody else touches, and the buffer is
+          // refilled only after the P*V product of this step has consumed them
+          const uint32_t a = lane_base + kColS + sbuf * 128 + kb_sel * 64;
 #pragma unroll
-            for (int cc = 0; cc < kCols / 32; ++cc)
-              tmem_ld32(a + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[cc * 32]));
-            tmem_ld_wait();
-            t_ld += FG_CLK() - tm0;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(PB_S_EMPTY + sbuf));   // scores are in registers: buffer reusable
-            ml_probs<FG_POLY_OF8, kCols>(r, pk, valid, c, t_row);
-          } else {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(PB_S_EMPTY + sbuf));
+          for (int ch = 0; ch < 2; ++ch) {
+            const int valid = max(0, min(32, valid_kb - ch * 32));
+            uint32_t pk[16];
+            if (valid > 0 && !(p.debug & 4)) {           // warp-uniform
+              uint32_t r[32];
+              tmem_ld32(a + ch * 32, r);
+              tmem_ld_wait();
+              ml_probs<FG_POLY_OF8, 32>(r, pk, valid, c, t_row);
+            } else {
 #pragma unroll
-            for (int i = 0; i < kCols / 2; ++i) pk[i] = 0u;
+              for (int i = 0; i < 16; ++i) pk[i] = 0u;
+            }
+            tmem_st16(a + ch * 16, pk);
           }
           t_math += FG_CLK() - tm0;
-          // P[s&1] was last read by the P*V product of step s-2
-          if (s >= 2) FG_TW(w_pe, ok = mbar_wait(bar(PB_P_EMPTY + sbuf), ((s >> 1) - 1) & 1, ab, p.err, 1404));
-          if (!ok) break;
-          tc_fence_after();
           long long ts0 = FG_CLK();
-          if constexpr (kCols == 64) tmem_st32(lane_base + kColP + sbuf * 64 + wg * 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
-          else tmem_st16(lane_base + kColP + sbuf * 64 + wg * 16, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(PB_P_FULL + sbuf * Cfg::kSmWGs + wg));
+          if (lane == 0) mbar_arrive(bar(PB_P_FULL + (s % 6) * 2 + kb_sel));
           t_st += FG_CLK() - ts0;
-          if (j == 0 && pe) {
+          if (pe) {                                      // pending rows of the previous item
             epilogue();
             if (!ok) break;
           }
