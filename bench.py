@@ -373,9 +373,9 @@ def main():
                 "speedup_gap": (1.0 / density) / (ms_full / ms_step)},
         }
         # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
-        # profiles/sparse_ml_persistent_c3_16heads.md (16 heads: 305 MB), scaled by heads
+        # profiles/sparse_ml_persistent_c3_16heads.md (16 heads: 312 MB), scaled by heads
         if args.workload == "c3":
-            line["roofline"]["traffic"] = 305.0e6 * (w.B * w.H) / 16.0
+            line["roofline"]["traffic"] = 312.0e6 * (w.B * w.H) / 16.0
         if world == 1 and not args.no_cpu_baseline:
             r = run_cpu(w, steps=2, warmup=1, budget_s=25.0)
             line["cpu_baseline"] = {k_: r[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
