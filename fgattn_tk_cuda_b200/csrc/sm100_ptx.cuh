@@ -114,6 +114,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, AbortSt
   }
 }
 
+// Same bounded wait for roles whose waits are long and not latency critical (TMA producers, the
+// scheduler): the warp sleeps between polls instead of occupying an issue slot.
+#ifndef FG_WAIT_SLEEP_NS
+#define FG_WAIT_SLEEP_NS 64
+#endif
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    __nanosleep(FG_WAIT_SLEEP_NS);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (ab->flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        ab->flag = 1;
+        if (err) atomicCAS(err, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 // Whole-warp variant for warp-uniform control flow (the UMMA issuer): every lane polls, the verdict
 // is made uniform so that a following elect.sync sees a converged warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {

@@ -206,7 +206,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     for (;; ++it) {
       const int lb = it % NLB;
       bool ok = true;
-      if (it >= NLB) FG_TW(w_le, ok = mbar_wait(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001));
+      if (it >= NLB) FG_TW(w_le, ok = mbar_wait_relaxed(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001));
       if (!ok) break;
       int g = 0;
       if (lane == 0) g = atomicAdd(p.queue, 1);
@@ -304,7 +304,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       bool ok = true;
       for (int it = 0; ok; ++it) {
         const int lb = it % NLB;
-        ok = mbar_wait(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1102);
+        ok = mbar_wait_relaxed(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1102);
         if (!ok) break;
         const int n = info[lb].n_steps;
         if (n < 0) break;
@@ -312,7 +312,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           const int bh = info[lb].bh, pair = info[lb].pair;
           if (is_k) {
             const int qb = u & 1;
-            if (u >= 2) ok = mbar_wait(bar(PB_Q_EMPTY + qb), ((u >> 1) - 1) & 1, ab, p.err, 1103);
+            if (u >= 2) ok = mbar_wait_relaxed(bar(PB_Q_EMPTY + qb), ((u >> 1) - 1) & 1, ab, p.err, 1103);
             if (!ok) break;
             mbar_arrive_expect_tx(bar(PB_Q_FULL + qb), Cfg::kTileBytes);
             for (int h = 0; h < Cfg::kHalves; ++h)
@@ -323,7 +323,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           for (int j = 0; j < n && ok; ++j, ++s) {
             const int kb0 = entry_kb(list[2 * j]), kb1 = entry_kb(list[2 * j + 1]);
             const int st = s % n_stages, f = s / n_stages;
-            if (f > 0) ok = mbar_wait(bar(empty0 + st), (f - 1) & 1, ab, p.err, 1104);
+            if (f > 0) ok = mbar_wait_relaxed(bar(empty0 + st), (f - 1) & 1, ab, p.err, 1104);
             if (!ok) break;
             const uint32_t dst = ring + st * Cfg::kTileBytes, full_bar = bar(full0 + st);
             if (p.debug & 1) {
