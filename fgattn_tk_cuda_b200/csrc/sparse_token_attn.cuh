@@ -1,6 +1,6 @@
 // Sparse attention over key-TOKEN lists at the reference granularity (128-row query blocks).
 // For each query block the listed K/V rows are gathered 128 at a time into swizzled shared-memory
-// tiles (16-byte cp.async per chunk, three gather warps), and the flash-attention step over the
+// tiles (16-byte cp.async per chunk, whole rows per warp-wide copy, three gather warps), and the flash-attention step over the
 // gathered keys runs on tcgen05 with an online (renormalising) softmax.  A CTA runs two query
 // blocks ("slots") against one tensor pipe; their K/V tiles share one ring in consumption order.
 // List entries >= the number of key rows, and slots past the count, are masked out.
@@ -110,26 +110,40 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
                       bh);
     }
     __syncwarp();
-    const int gtid = (warp == 8) ? lane : (warp - 9) * 32 + lane;     // 0..95
+    const int gw = (warp == 8) ? 0 : warp - 9;                         // gather warp 0..2
     constexpr int kChunksPerRow = D / 8;                               // 16-byte chunks per row
+    constexpr int kRowsPerInstr = 32 / kChunksPerRow;                  // rows one warp-wide copy covers
+    // rows of a 128-token tile are dealt to the three gather warps in contiguous runs of 44 / 44 / 40;
+    // a lane keeps the token ids of run rows `lane` and `lane + 32`
+    const int row0 = gw * 44, nrows = (gw == 2) ? 40 : 44;
+    const int sub = lane / kChunksPerRow, ch = lane % kChunksPerRow;
     int idx = 0;
     bool ok = true;
     int pending_stage = -1;                                            // tile whose copies are in flight
-    auto gather_tile = [&](const __nv_bfloat16* base, int t, int j) {
+    int tokA[2] = {0, 0}, tokB[2] = {0, 0};                            // token ids of the slot's current step
+    auto load_tokens = [&](int t, int j) {
+      const int pa = j * 128 + row0 + lane, pb = pa + 32;
+      int a = (pa < cnt[t]) ? lst[t][pa] : 0;
+      int b = (lane + 32 < nrows && pb < cnt[t]) ? lst[t][pb] : 0;
+      if (a < 0 || a >= p.S) a = 0;                                    // masked column: any finite row will do
+      if (b < 0 || b >= p.S) b = 0;
+      tokA[t] = a;
+      tokB[t] = b;
+    };
+    // Each copy instruction moves whole rows: 16 (D = 128) or 8 (D = 64) neighbouring lanes fetch the
+    // consecutive 16-byte chunks of one row, so a warp-wide copy asks L2 for full 128-byte lines
+    // instead of 32 separate sectors.
+    auto gather_tile = [&](const __nv_bfloat16* base, int t) {
       const int st = idx % Cfg::kStages, f = idx / Cfg::kStages;
       if (f > 0) ok = mbar_wait(bar(TB_EMPTY + st), (f - 1) & 1, ab, p.err, 701);
       if (!ok) return;
-      const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
-      // one thread per gathered row: the index is read once, then the row's 16-byte chunks follow
-      // (measured faster than 16 lanes per row, where every copy waits for its own index load)
-      for (int row = gtid; row < 128; row += Cfg::kGatherThreads) {
-        const int pos = j * 128 + row;
-        int tok = (pos < cnt[t]) ? lst[t][pos] : 0;
-        if (tok < 0 || tok >= p.S) tok = 0;                            // masked column: any finite row will do
-        const __nv_bfloat16* src = base + (size_t(bh) * p.S + tok) * D;
-#pragma unroll
-        for (int ch = 0; ch < kChunksPerRow; ++ch)
-          cp_async_16(dst + (ch >> 3) * 16384 + sw128_offset(row, ch & 7), src + ch * 8);
+      const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes + (ch >> 3) * 16384;
+      const __nv_bfloat16* src0 = base + size_t(bh) * p.S * D + ch * 8;
+      for (int r = 0; r < nrows; r += kRowsPerInstr) {                 // nrows is a multiple of 4
+        const int lr = r + sub;                                        // run row of this lane
+        const int ta = __shfl_sync(0xffffffffu, tokA[t], lr & 31), tb = __shfl_sync(0xffffffffu, tokB[t], lr & 31);
+        const int tok = (lr < 32) ? ta : tb;
+        cp_async_16(dst + sw128_offset(row0 + lr, ch & 7), src0 + size_t(tok) * D);
       }
       cp_async_commit();
       if (pending_stage >= 0) {
@@ -140,13 +154,17 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       pending_stage = st;
       ++idx;
     };
-    if (nst[0] > 0) gather_tile(p.k, 0, 0);
-    if (nst[1] > 0 && ok) gather_tile(p.k, 1, 0);
+    // order: K(0,0) K(1,0), then per step V(t,j) K(t,j+1); the ids of step j serve K(t,j) and V(t,j)
+    if (nst[0] > 0) { load_tokens(0, 0); gather_tile(p.k, 0); }
+    if (nst[1] > 0 && ok) { load_tokens(1, 0); gather_tile(p.k, 1); }
     for (int j = 0; j < n_max && ok; ++j) {
       for (int t = 0; t < 2 && ok; ++t) {
         if (j < nst[t]) {
-          gather_tile(p.v, t, j);
-          if (ok && j + 1 < nst[t]) gather_tile(p.k, t, j + 1);
+          gather_tile(p.v, t);
+          if (ok && j + 1 < nst[t]) {
+            load_tokens(t, j + 1);
+            gather_tile(p.k, t);
+          }
         }
       }
     }

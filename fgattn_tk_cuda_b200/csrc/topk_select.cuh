@@ -195,7 +195,8 @@ constexpr int kSelBins = 2048;
 // smallest and largest key of the row; each following sweep histograms the keys of the current
 // interval into 2048 equal bins (a plain byte-wise radix would put almost every score of a row into
 // two or three bins of its leading byte and serialise the shared-memory counters), picks the bin
-// that holds the k-th largest and narrows the interval to it, until the bins are one key wide.
+// that holds the k-th largest and narrows the interval to it, until the bin and everything above it
+// fit the sort buffer (usually after one histogram sweep) or the bins are one key wide.
 __global__ void __launch_bounds__(kSelThreads)
 topk_select_kernel(const float* __restrict__ scores, int s_stride, int n, int k, int k_pow2, int* __restrict__ idx,
                    int* __restrict__ cnt, int list_stride) {
@@ -289,9 +290,12 @@ topk_select_kernel(const float* __restrict__ scores, int s_stride, int n, int k,
       }
     }
     __syncthreads();
-    if (shift == 0) break;
+    // stop as soon as everything from the chosen bin upwards fits the sort buffer: the sort then
+    // orders the bin's entries too and the first k sorted entries are the answer
+    if (shift == 0 || (k - s_rem) + s_ties <= k_pow2) break;
   }
-  const uint32_t kth = s_lo;                             // s_rem of the s_ties entries equal to kth are needed
+  const uint32_t kth = s_lo;                             // lowest key taken; s_rem of the s_ties entries in
+                                                         // [kth, s_hi] are needed (s_hi == kth after a full narrowing)
   const int rem = s_rem, n_gt = k - rem;
   __syncthreads();
 
