@@ -26,24 +26,24 @@ PROTOTYPES = {
     "fgattn_status_string": (C.c_char_p, [_i]),
     "fgattn_last_cuda_error": (_i, []),
     "fgattn_check": (_i, [_vp, C.POINTER(_i)]),
-    "fgattn_full_attn": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
-    "fgattn_fullattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
-    "fgattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
-    "fgattn_booleanmask_128": (_i, [_vp, _f, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_full_attn": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_fullattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_booleanmask_128": (_i, [_vp, _f, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_booleanmask_to_indexmask": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "fgattn_all_index_mask": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "fgattn_sp_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_sp_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_block_scratch_bytes": (_sz, [_i, _i, _i, _i]),
-    "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f, _vp,
+    "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _f, _vp,
                                       _sz, _vp]),
     "fgattn_block_index_lists_noalloc": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f,
                                               _vp]),
-    "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _sz,
+    "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
-    "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
-    "fgattn_topk_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
-    "fgattn_topk_indices": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_topk_scratch_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
+    "fgattn_topk_indices": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "fgattn_pack_mask": (_i, [_vp, _vp, _i, _ll, _i, _vp]),
     "fgattn_unpack_mask": (_i, [_vp, _i, _vp, _ll, _i, _vp]),
     "fgattn_packedmask_to_indexmask": (_i, [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp]),
@@ -114,7 +114,8 @@ def full_attn(o, q, k, v, kv_seq_len=None, scale=0.0):
     _check_qkv(o, q, k, v)
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
-        _call("fgattn_full_attn", _ptr(o), _ptr(q), _ptr(k), _ptr(v), B, H, S, D, kv_seq_len or S, scale, _stream(q))
+        _call("fgattn_full_attn", _ptr(o), _ptr(q), _ptr(k), _ptr(v), B, H, S, D, k.shape[2],
+              kv_seq_len or k.shape[2], scale, _stream(q))
 
 
 def fullattn_maxq_denom(o, max_q, denom, q, k, v, kv_seq_len=None, scale=0.0):
@@ -122,15 +123,15 @@ def fullattn_maxq_denom(o, max_q, denom, q, k, v, kv_seq_len=None, scale=0.0):
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
         _call("fgattn_fullattn_maxq_denom", _ptr(o), _ptr(max_q), _ptr(denom), _ptr(q), _ptr(k), _ptr(v), B, H, S, D,
-              kv_seq_len or S, scale, _stream(q))
+              k.shape[2], kv_seq_len or k.shape[2], scale, _stream(q))
 
 
 def maxq_denom(max_q, denom, q, k, kv_seq_len=None, scale=0.0):
     _check_qkv(q, k)
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
-        _call("fgattn_maxq_denom", _ptr(max_q), _ptr(denom), _ptr(q), _ptr(k), B, H, S, D, kv_seq_len or S, scale,
-              _stream(q))
+        _call("fgattn_maxq_denom", _ptr(max_q), _ptr(denom), _ptr(q), _ptr(k), B, H, S, D, k.shape[2],
+              kv_seq_len or k.shape[2], scale, _stream(q))
 
 
 def booleanmask_128(booleanmask, max_q, denom, q, k, threshold, kv_seq_len=None, scale=0.0):
@@ -138,7 +139,7 @@ def booleanmask_128(booleanmask, max_q, denom, q, k, threshold, kv_seq_len=None,
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
         _call("fgattn_booleanmask_128", _ptr(booleanmask), float(threshold), booleanmask.shape[3], _ptr(max_q),
-              _ptr(denom), _ptr(q), _ptr(k), B, H, S, D, kv_seq_len or S, scale, _stream(q))
+              _ptr(denom), _ptr(q), _ptr(k), B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale, _stream(q))
 
 
 def booleanmask_to_indexmask(kv_indices, kv_num_indices, booleanmask, seq):
@@ -159,7 +160,7 @@ def sp_attn(o, q, k, v, kv_indices, kv_num_indices, scale=0.0):
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kv_indices), _ptr(kv_num_indices),
-              kv_indices.shape[3], B, H, S, D, scale, _stream(q))
+              kv_indices.shape[3], B, H, S, D, k.shape[2], scale, _stream(q))
 
 
 def block_scratch_bytes(B, H, S, kv_seq_len=None) -> int:
@@ -172,8 +173,8 @@ def block_index_lists(kb_indices, kb_counts, max_q, denom, q, k, threshold, scra
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
         _call("fgattn_block_index_lists", _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3], _ptr(max_q),
-              _ptr(denom), _ptr(o), _ptr(q), _ptr(k), _ptr(v), float(threshold), B, H, S, D, kv_seq_len or S, scale,
-              _ptr(scratch), scratch.numel() * scratch.element_size(), _stream(q))
+              _ptr(denom), _ptr(o), _ptr(q), _ptr(k), _ptr(v), float(threshold), B, H, S, D, k.shape[2],
+              kv_seq_len or k.shape[2], scale, _ptr(scratch), scratch.numel() * scratch.element_size(), _stream(q))
 
 
 NOALLOC_SCRATCH_BYTES = 64 << 20
@@ -202,7 +203,8 @@ def sp_attn_blocks_ml(o, q, k, v, kb_indices, kb_counts, max_q, denom, kv_seq_le
         workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn_blocks_ml", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
-              kb_indices.shape[3], _ptr(max_q), _ptr(denom), B, H, S, D, kv_seq_len or S, scale, _ptr(workspace),
+              kb_indices.shape[3], _ptr(max_q), _ptr(denom), B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale,
+              _ptr(workspace),
               workspace.numel() * workspace.element_size(), _stream(q))
 
 
@@ -211,7 +213,7 @@ def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn_blocks", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
-              kb_indices.shape[3], B, H, S, D, kv_seq_len or S, scale, _stream(q))
+              kb_indices.shape[3], B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale, _stream(q))
 
 
 # ---- one-bit-per-entry masks ----------------------------------------------------------------------
@@ -259,8 +261,8 @@ def indexmask_to_packedmask(packed, indices, num_indices):
 
 
 # ---- top-k selector ---------------------------------------------------------------------------------
-def topk_scratch_bytes(B, H, S, D, blocksz) -> int:
-    return int(lib().fgattn_topk_scratch_bytes(B, H, S, D, blocksz))
+def topk_scratch_bytes(B, H, S, D, blocksz, kv_seq_len=None) -> int:
+    return int(lib().fgattn_topk_scratch_bytes(B, H, S, D, blocksz, kv_seq_len or S))
 
 
 def topk_indices(kv_indices, kv_num_indices, q, k, select_k, blocksz=128, kv_seq_len=None, scale=0.0, scratch=None):
@@ -268,8 +270,9 @@ def topk_indices(kv_indices, kv_num_indices, q, k, select_k, blocksz=128, kv_seq
     _check_qkv(q, k)
     B, H, S, D = q.shape
     if scratch is None:
-        scratch = torch.empty(topk_scratch_bytes(B, H, S, D, blocksz), dtype=torch.uint8, device=q.device)
+        scratch = torch.empty(topk_scratch_bytes(B, H, S, D, blocksz, kv_seq_len or k.shape[2]), dtype=torch.uint8,
+                              device=q.device)
     with torch.cuda.device(q.device):
         _call("fgattn_topk_indices", _ptr(kv_indices), _ptr(kv_num_indices), kv_indices.shape[3], _ptr(q), _ptr(k),
-              int(select_k), B, H, S, D, int(blocksz), kv_seq_len or S, scale, _ptr(scratch),
+              int(select_k), B, H, S, D, int(blocksz), k.shape[2], kv_seq_len or k.shape[2], scale, _ptr(scratch),
               scratch.numel() * scratch.element_size(), _stream(q))

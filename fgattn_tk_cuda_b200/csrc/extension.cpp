@@ -32,7 +32,7 @@ void full_attn(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Tensor 
   check_bf16_4d(o, "o"); check_bf16_4d(q, "q"); check_bf16_4d(k, "k"); check_bf16_4d(v, "v");
   c10::cuda::CUDAGuard guard(q.device());
   check_status(fgattn_full_attn(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), q.size(0), q.size(1),
-                                q.size(2), q.size(3), k.size(2), 0.f, stream_of(q)), "full_attn");
+                                q.size(2), q.size(3), k.size(2), k.size(2), 0.f, stream_of(q)), "full_attn");
 }
 
 void all_index_mask(torch::Tensor kv_indices, torch::Tensor kv_num_indices, int64_t batch, int64_t heads,
@@ -51,7 +51,7 @@ void sp_attn(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Tensor v,
   c10::cuda::CUDAGuard guard(q.device());
   check_status(fgattn_sp_attn(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), kv_indices.data_ptr<int>(),
                               kv_num_indices.data_ptr<int>(), int(kv_indices.size(3)), q.size(0), q.size(1),
-                              q.size(2), q.size(3), 0.f, stream_of(q)), "sp_attn");
+                              q.size(2), q.size(3), k.size(2), 0.f, stream_of(q)), "sp_attn");
 }
 
 void fullattn_maxq_denom(torch::Tensor o, torch::Tensor o_max_q, torch::Tensor o_denom, torch::Tensor q,
@@ -61,7 +61,7 @@ void fullattn_maxq_denom(torch::Tensor o, torch::Tensor o_max_q, torch::Tensor o
   c10::cuda::CUDAGuard guard(q.device());
   check_status(fgattn_fullattn_maxq_denom(o.data_ptr(), o_max_q.data_ptr<float>(), o_denom.data_ptr<float>(),
                                           q.data_ptr(), k.data_ptr(), v.data_ptr(), q.size(0), q.size(1), q.size(2),
-                                          q.size(3), k.size(2), 0.f, stream_of(q)), "fullattn_maxq_denom");
+                                          q.size(3), k.size(2), k.size(2), 0.f, stream_of(q)), "fullattn_maxq_denom");
 }
 
 void maxq_denom(torch::Tensor o_max_q, torch::Tensor o_denom, torch::Tensor q, torch::Tensor k) {
@@ -69,7 +69,7 @@ void maxq_denom(torch::Tensor o_max_q, torch::Tensor o_denom, torch::Tensor q, t
   check_dtype(o_max_q, at::kFloat, "o_max_q"); check_dtype(o_denom, at::kFloat, "o_denom");
   c10::cuda::CUDAGuard guard(q.device());
   check_status(fgattn_maxq_denom(o_max_q.data_ptr<float>(), o_denom.data_ptr<float>(), q.data_ptr(), k.data_ptr(),
-                                 q.size(0), q.size(1), q.size(2), q.size(3), k.size(2), 0.f, stream_of(q)),
+                                 q.size(0), q.size(1), q.size(2), q.size(3), k.size(2), k.size(2), 0.f, stream_of(q)),
                "maxq_denom");
 }
 
@@ -81,7 +81,7 @@ void booleanmask_128(torch::Tensor booleanmask, torch::Tensor o_max_q, torch::Te
   c10::cuda::CUDAGuard guard(q.device());
   check_status(fgattn_booleanmask_128(booleanmask.data_ptr<int>(), float(threshold), int(booleanmask.size(3)),
                                       o_max_q.data_ptr<float>(), o_denom.data_ptr<float>(), q.data_ptr(),
-                                      k.data_ptr(), q.size(0), q.size(1), q.size(2), q.size(3), k.size(2), 0.f,
+                                      k.data_ptr(), q.size(0), q.size(1), q.size(2), q.size(3), k.size(2), k.size(2), 0.f,
                                       stream_of(q)), "booleanmask_128");
 }
 
@@ -111,7 +111,7 @@ void block_index_lists(torch::Tensor kb_indices, torch::Tensor kb_counts, torch:
                                         o_max_q.data_ptr<float>(), o_denom.data_ptr<float>(),
                                         o ? o->data_ptr() : nullptr, q.data_ptr(), k.data_ptr(),
                                         v ? v->data_ptr() : nullptr, float(threshold), q.size(0), q.size(1), q.size(2),
-                                        q.size(3), k.size(2), 0.f, scratch.data_ptr(),
+                                        q.size(3), k.size(2), k.size(2), 0.f, scratch.data_ptr(),
                                         size_t(scratch.numel()) * scratch.element_size(), stream_of(q)),
                "block_index_lists");
 }
@@ -128,7 +128,7 @@ void sp_attn_blocks_ml(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch:
   check_status(fgattn_sp_attn_blocks_ml(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                         kb_indices.data_ptr<int>(), kb_counts.data_ptr<int>(), int(kb_indices.size(3)),
                                         max_q.data_ptr<float>(), denom.data_ptr<float>(), q.size(0), q.size(1),
-                                        q.size(2), q.size(3), k.size(2), 0.f, ws.data_ptr(), size_t(ws_bytes),
+                                        q.size(2), q.size(3), k.size(2), k.size(2), 0.f, ws.data_ptr(), size_t(ws_bytes),
                                         stream_of(q)), "sp_attn_blocks_ml");
 }
 
@@ -139,7 +139,7 @@ void sp_attn_blocks(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Te
   c10::cuda::CUDAGuard guard(q.device());
   check_status(fgattn_sp_attn_blocks(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                      kb_indices.data_ptr<int>(), kb_counts.data_ptr<int>(), int(kb_indices.size(3)),
-                                     q.size(0), q.size(1), q.size(2), q.size(3), k.size(2), 0.f, stream_of(q)),
+                                     q.size(0), q.size(1), q.size(2), q.size(3), k.size(2), k.size(2), 0.f, stream_of(q)),
                "sp_attn_blocks");
 }
 
@@ -203,11 +203,13 @@ void topk_indices(torch::Tensor kv_indices, torch::Tensor kv_num_indices, torch:
   check_dtype(kv_indices, at::kInt, "kv_indices"); check_dtype(kv_num_indices, at::kInt, "kv_num_indices");
   TORCH_CHECK(kv_indices.dim() == 4, "kv_indices must be [B, H, blocks, stride]");
   c10::cuda::CUDAGuard guard(q.device());
-  const int64_t bytes = int64_t(fgattn_topk_scratch_bytes(q.size(0), q.size(1), q.size(2), q.size(3), int(blocksz)));
+  const int64_t bytes = int64_t(fgattn_topk_scratch_bytes(q.size(0), q.size(1), q.size(2), q.size(3), int(blocksz),
+                                                          int(k.size(2))));
   torch::Tensor scratch = torch::empty({bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
   check_status(fgattn_topk_indices(kv_indices.data_ptr<int>(), kv_num_indices.data_ptr<int>(), int(kv_indices.size(3)),
                                    q.data_ptr(), k.data_ptr(), int(select_k), q.size(0), q.size(1), q.size(2),
-                                   q.size(3), int(blocksz), k.size(2), 0.f, scratch.data_ptr(), size_t(bytes),
+                                   q.size(3), int(blocksz), k.size(2), k.size(2), 0.f, scratch.data_ptr(),
+                                   size_t(bytes),
                                    stream_of(q)), "topk_indices");
 }
 

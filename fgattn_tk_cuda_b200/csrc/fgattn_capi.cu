@@ -49,11 +49,12 @@ int get_err_word(int** out) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int check_qk(const void* q, const void* k, int B, int H, int S, int D, int kv_len) {
+// S = query rows, kv_rows = rows of the k / v tensors per head, kv_len = leading k / v rows that take part
+int check_qk(const void* q, const void* k, int B, int H, int S, int D, int kv_rows, int kv_len) {
   if (!q || !k) return FGATTN_INVALID_ARGUMENT;
-  if (B <= 0 || H <= 0 || S <= 0) return FGATTN_INVALID_ARGUMENT;
+  if (B <= 0 || H <= 0 || S <= 0 || kv_rows <= 0) return FGATTN_INVALID_ARGUMENT;
   if (D != 64 && D != 128) return FGATTN_UNSUPPORTED;
-  if (kv_len < 1 || kv_len > S) return FGATTN_INVALID_ARGUMENT;
+  if (kv_len < 1 || kv_len > kv_rows) return FGATTN_INVALID_ARGUMENT;
   if ((long long)B * H > 65535) return FGATTN_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(k)) return FGATTN_MISALIGNED;
   return FGATTN_OK;
@@ -95,13 +96,13 @@ struct DenseSetup {
   fg::DenseParams p;
 };
 
-int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int B, int H, int S, int D, int kv_len,
-                float scale) {
-  int r = check_qk(q, k, B, H, S, D, kv_len);
+int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int B, int H, int S, int D, int kv_rows,
+                int kv_len, float scale) {
+  int r = check_qk(q, k, B, H, S, D, kv_rows, kv_len);
   if (r) return r;
   if (v && !aligned16(v)) return FGATTN_MISALIGNED;
-  if (fg::make_qkv_map(&s.mq, q, B * H, S, D, 128) || fg::make_qkv_map(&s.mk, k, B * H, S, D, 128) ||
-      fg::make_qkv_map(&s.mv, v ? v : k, B * H, S, D, 128))
+  if (fg::make_qkv_map(&s.mq, q, B * H, S, D, 128) || fg::make_qkv_map(&s.mk, k, B * H, kv_rows, D, 128) ||
+      fg::make_qkv_map(&s.mv, v ? v : k, B * H, kv_rows, D, 128))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   memset(&s.p, 0, sizeof(s.p));
   s.p.S = S;
@@ -115,9 +116,9 @@ int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int 
 
 template <bool RENORM>
 int launch_sparse(void* o, const void* q, const void* k, const void* v, const int* kb_idx, const int* kb_cnt,
-                  int list_stride, const float* max_q, const float* denom, int B, int H, int S, int D, int kv_len,
-                  float scale, cudaStream_t st) {
-  int r = check_qk(q, k, B, H, S, D, kv_len);
+                  int list_stride, const float* max_q, const float* denom, int B, int H, int S, int D, int kv_rows,
+                  int kv_len, float scale, cudaStream_t st) {
+  int r = check_qk(q, k, B, H, S, D, kv_rows, kv_len);
   if (r) return r;
   if (!o || !v || !kb_idx || !kb_cnt) return FGATTN_INVALID_ARGUMENT;
   if (!RENORM && (!max_q || !denom)) return FGATTN_INVALID_ARGUMENT;
@@ -141,8 +142,8 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
   r = get_err_word(&p.err);
   if (r) return r;
   CUtensorMap mq, mk, mv;
-  if (fg::make_qkv_map(&mq, q, B * H, S, D, 128) || fg::make_qkv_map(&mk, k, B * H, S, D, 64) ||
-      fg::make_qkv_map(&mv, v, B * H, S, D, 64))
+  if (fg::make_qkv_map(&mq, q, B * H, S, D, 128) || fg::make_qkv_map(&mk, k, B * H, kv_rows, D, 64) ||
+      fg::make_qkv_map(&mv, v, B * H, kv_rows, D, 64))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   dim3 grid((S + 255) / 256, B * H, 1);
   if (D == 128) {
@@ -201,22 +202,23 @@ int fgattn_check(void* stream, int* code) {
 }
 
 int fgattn_full_attn(void* o, const void* q, const void* k, const void* v, int batch, int heads, int seq, int D,
-                     int kv_seq_len, float scale, void* stream) {
+                     int kv_rows, int kv_seq_len, float scale, void* stream) {
   if (!o || !v) return FGATTN_INVALID_ARGUMENT;
   if (!aligned16(o)) return FGATTN_MISALIGNED;
   DenseSetup s;
-  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_seq_len, scale);
+  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_rows, kv_seq_len, scale);
   if (r) return r;
   s.p.o = static_cast<__nv_bfloat16*>(o);
   return launch_dense<fg::kFull, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, static_cast<cudaStream_t>(stream));
 }
 
 int fgattn_fullattn_maxq_denom(void* o, float* max_q, float* denom, const void* q, const void* k, const void* v,
-                               int batch, int heads, int seq, int D, int kv_seq_len, float scale, void* stream) {
+                               int batch, int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale,
+                               void* stream) {
   if (!o || !v || !max_q || !denom) return FGATTN_INVALID_ARGUMENT;
   if (!aligned16(o)) return FGATTN_MISALIGNED;
   DenseSetup s;
-  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_seq_len, scale);
+  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_rows, kv_seq_len, scale);
   if (r) return r;
   s.p.o = static_cast<__nv_bfloat16*>(o);
   s.p.max_q = max_q;
@@ -225,10 +227,10 @@ int fgattn_fullattn_maxq_denom(void* o, float* max_q, float* denom, const void* 
 }
 
 int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, int batch, int heads, int seq, int D,
-                      int kv_seq_len, float scale, void* stream) {
+                      int kv_rows, int kv_seq_len, float scale, void* stream) {
   if (!max_q || !denom) return FGATTN_INVALID_ARGUMENT;
   DenseSetup s;
-  int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_seq_len, scale);
+  int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_rows, kv_seq_len, scale);
   if (r) return r;
   s.p.max_q = max_q;
   s.p.denom = denom;
@@ -236,12 +238,12 @@ int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, 
 }
 
 int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
-                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_seq_len,
-                           float scale, void* stream) {
+                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_rows,
+                           int kv_seq_len, float scale, void* stream) {
   if (!booleanmask || !max_q || !denom || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
   if (mask_stride < kv_seq_len) return FGATTN_INVALID_ARGUMENT;
   DenseSetup s;
-  int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_seq_len, scale);
+  int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_rows, kv_seq_len, scale);
   if (r) return r;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t n = size_t(batch) * heads * ((seq + 127) / 128) * mask_stride;
@@ -279,9 +281,9 @@ int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int h
 }
 
 int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
-                   const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, float scale,
-                   void* stream) {
-  int r = check_qk(q, k, batch, heads, seq, D, seq);
+                   const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, int kv_rows,
+                   float scale, void* stream) {
+  int r = check_qk(q, k, batch, heads, seq, D, kv_rows, kv_rows);
   if (r) return r;
   if (!o || !v || !kv_indices || !kv_num_indices || mask_stride < 1) return FGATTN_INVALID_ARGUMENT;
   if (!aligned16(o) || !aligned16(v)) return FGATTN_MISALIGNED;
@@ -293,6 +295,7 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
   p.kv_idx = kv_indices;
   p.kv_cnt = kv_num_indices;
   p.S = seq;
+  p.S_kv = kv_rows;
   p.nqb = (seq + 127) / 128;
   p.mask_stride = mask_stride;
   p.scale_log2 = resolve_scale_log2(scale, D);
@@ -326,13 +329,13 @@ size_t fgattn_block_scratch_bytes(int batch, int heads, int seq, int kv_seq_len)
 
 int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, float* max_q, float* denom, void* o,
                              const void* q, const void* k, const void* v, float threshold, int batch, int heads,
-                             int seq, int D, int kv_seq_len, float scale, void* scratch, size_t scratch_bytes,
-                             void* stream) {
+                             int seq, int D, int kv_rows, int kv_seq_len, float scale, void* scratch,
+                             size_t scratch_bytes, void* stream) {
   if (!kb_indices || !kb_counts || !max_q || !denom || !scratch || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
   if ((o == nullptr) != (v == nullptr)) return FGATTN_INVALID_ARGUMENT;
   if (o && !aligned16(o)) return FGATTN_MISALIGNED;
   DenseSetup s;
-  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_seq_len, scale);
+  int r = dense_setup(s, q, k, v, batch, heads, seq, D, kv_rows, kv_seq_len, scale);
   if (r) return r;
   const int nkb = s.p.nkb, nqb = (seq + 63) / 64;
   if (list_stride < nkb) return FGATTN_INVALID_ARGUMENT;
@@ -403,7 +406,7 @@ int fgattn_block_index_lists_noalloc(int* kb_indices, int* kb_counts, int list_s
   if (!kb_indices || !kb_counts || !max_q || !denom || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
   if ((o == nullptr) != (v == nullptr)) return FGATTN_INVALID_ARGUMENT;
   if (o && !aligned16(o)) return FGATTN_MISALIGNED;
-  int r = check_qk(q, k, batch, heads, seq, D, kv_seq_len);
+  int r = check_qk(q, k, batch, heads, seq, D, seq, kv_seq_len);
   if (r) return r;
   if (v && !aligned16(v)) return FGATTN_MISALIGNED;
   const int nkb = (kv_seq_len + 63) / 64, nqb = (seq + 63) / 64, s_pad = ((seq + 127) / 128) * 128;
@@ -457,9 +460,9 @@ size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq) {
 
 int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                              const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
-                             int heads, int seq, int D, int kv_seq_len, float scale, void* workspace,
+                             int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream) {
-  int r = check_qk(q, k, batch, heads, seq, D, kv_seq_len);
+  int r = check_qk(q, k, batch, heads, seq, D, kv_rows, kv_seq_len);
   if (r) return r;
   if (!o || !v || !kb_indices || !kb_counts || !max_q || !denom || !workspace || list_stride < 1)
     return FGATTN_INVALID_ARGUMENT;
@@ -492,15 +495,15 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
   r = get_err_word(&p.err);
   if (r) return r;
   CUtensorMap mq, mk, mv;
-  if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128) || fg::make_qkv_map(&mk, k, batch * heads, seq, D, 64) ||
-      fg::make_qkv_map(&mv, v, batch * heads, seq, D, 64))
+  if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128) || fg::make_qkv_map(&mk, k, batch * heads, kv_rows, D, 64) ||
+      fg::make_qkv_map(&mv, v, batch * heads, kv_rows, D, 64))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   int dev = 0, sms = 0;
   FG_CUDA(cudaGetDevice(&dev));
   FG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   // heads per queue group: enough items to balance the SMs (about six per SM), K/V of a group <= 64 MiB
   const int n_units = batch * heads;
-  const size_t kv_bytes_per_unit = size_t(4) * seq * D;
+  const size_t kv_bytes_per_unit = size_t(4) * kv_rows * D;
   int group_heads = (6 * sms + p.npairs - 1) / p.npairs;
   group_heads = std::min<int>(group_heads, int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit)));
   if (const char* gh = getenv("FGATTN_GROUP_HEADS")) group_heads = atoi(gh);   // tuning override
@@ -588,10 +591,10 @@ int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, co
 }
 
 int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
-                          const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_seq_len,
-                          float scale, void* stream) {
+                          const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_rows,
+                          int kv_seq_len, float scale, void* stream) {
   return launch_sparse<true>(o, q, k, v, kb_indices, kb_counts, list_stride, nullptr, nullptr, batch, heads, seq, D,
-                             kv_seq_len, scale, static_cast<cudaStream_t>(stream));
+                             kv_rows, kv_seq_len, scale, static_cast<cudaStream_t>(stream));
 }
 
 // ---- top-k selector ------------------------------------------------------------------------------
@@ -599,24 +602,25 @@ namespace {
 size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 }  // namespace
 
-size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz) {
-  if (batch <= 0 || heads <= 0 || seq <= 0 || D <= 0 || blocksz <= 0) return 0;
+size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz, int kv_seq_len) {
+  if (batch <= 0 || heads <= 0 || seq <= 0 || D <= 0 || blocksz <= 0 || kv_seq_len <= 0) return 0;
   const size_t bh = size_t(batch) * heads, nblk = size_t((seq + blocksz - 1) / blocksz);
-  const size_t s_stride = size_t((seq + 127) / 128) * 128;
+  const size_t s_stride = size_t((kv_seq_len + 127) / 128) * 128;
   return 2 * align256(bh * nblk * D * 2) + bh * nblk * s_stride * sizeof(float);
 }
 
 int fgattn_topk_indices(int* kv_indices, int* kv_num_indices, int list_stride, const void* q, const void* k,
-                        int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_seq_len, float scale,
-                        void* scratch, size_t scratch_bytes, void* stream) {
-  int r = check_qk(q, k, batch, heads, seq, D, kv_seq_len);
+                        int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_rows, int kv_seq_len,
+                        float scale, void* scratch, size_t scratch_bytes, void* stream) {
+  int r = check_qk(q, k, batch, heads, seq, D, kv_rows, kv_seq_len);
   if (r) return r;
   if (!kv_indices || !kv_num_indices || !scratch || blocksz < 1) return FGATTN_INVALID_ARGUMENT;
   if (select_k < 1 || select_k > kv_seq_len || list_stride < select_k) return FGATTN_INVALID_ARGUMENT;
   if (select_k > 8192) return FGATTN_UNSUPPORTED;          // the selected pairs are sorted in shared memory
   if (!aligned16(scratch)) return FGATTN_MISALIGNED;
-  if (scratch_bytes < fgattn_topk_scratch_bytes(batch, heads, seq, D, blocksz)) return FGATTN_SCRATCH_TOO_SMALL;
-  const int bh = batch * heads, nblk = (seq + blocksz - 1) / blocksz, s_stride = ((seq + 127) / 128) * 128;
+  if (scratch_bytes < fgattn_topk_scratch_bytes(batch, heads, seq, D, blocksz, kv_seq_len))
+    return FGATTN_SCRATCH_TOO_SMALL;
+  const int bh = batch * heads, nblk = (seq + blocksz - 1) / blocksz, s_stride = ((kv_seq_len + 127) / 128) * 128;
   if ((long long)bh * nblk > 2147483647LL || nblk > 65535 * 128) return FGATTN_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   char* base = static_cast<char*>(scratch);
@@ -634,7 +638,7 @@ int fgattn_topk_indices(int* kv_indices, int* kv_num_indices, int list_stride, c
   if (r) return r;
   CUtensorMap m_hi, m_lo, mk;
   if (fg::make_qkv_map(&m_hi, qm_hi, bh, nblk, D, 128) || fg::make_qkv_map(&m_lo, qm_lo, bh, nblk, D, 128) ||
-      fg::make_qkv_map(&mk, k, bh, seq, D, 128))
+      fg::make_qkv_map(&mk, k, bh, kv_rows, D, 128))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   const dim3 g_mean(nblk, bh), g_sc(s_stride / 128, (nblk + 127) / 128, bh);
   if (D == 128) {

@@ -17,7 +17,7 @@ struct TokenParams {
   const int* kv_idx;        // [BH, nqb128, mask_stride]
   const int* kv_cnt;        // [BH, nqb128]
   int* err;
-  int S, nqb, mask_stride;
+  int S, S_kv, nqb, mask_stride;   // query rows, rows of k / v per head
   float scale_log2;
 };
 
@@ -125,8 +125,8 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       const int pa = j * 128 + row0 + lane, pb = pa + 32;
       int a = (pa < cnt[t]) ? lst[t][pa] : 0;
       int b = (lane + 32 < nrows && pb < cnt[t]) ? lst[t][pb] : 0;
-      if (a < 0 || a >= p.S) a = 0;                                    // masked column: any finite row will do
-      if (b < 0 || b >= p.S) b = 0;
+      if (a < 0 || a >= p.S_kv) a = 0;                                    // masked column: any finite row will do
+      if (b < 0 || b >= p.S_kv) b = 0;
       tokA[t] = a;
       tokB[t] = b;
     };
@@ -138,7 +138,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       if (f > 0) ok = mbar_wait(bar(TB_EMPTY + st), (f - 1) & 1, ab, p.err, 701);
       if (!ok) return;
       const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes + (ch >> 3) * 16384;
-      const __nv_bfloat16* src0 = base + size_t(bh) * p.S * D + ch * 8;
+      const __nv_bfloat16* src0 = base + size_t(bh) * p.S_kv * D + ch * 8;
       for (int r = 0; r < nrows; r += kRowsPerInstr) {                 // nrows is a multiple of 4
         const int lr = r + sub;                                        // run row of this lane
         const int ta = __shfl_sync(0xffffffffu, tokA[t], lr & 31), tb = __shfl_sync(0xffffffffu, tokB[t], lr & 31);
@@ -242,7 +242,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       for (int w = 0; w < 4; ++w) {
         const int pos = j * 128 + w * 32 + lane;
         const int tok = (pos < cnt[t]) ? lst[t][pos] : -1;
-        live[w] = __ballot_sync(0xffffffffu, tok >= 0 && tok < p.S);
+        live[w] = __ballot_sync(0xffffffffu, tok >= 0 && tok < p.S_kv);
       }
       ok = mbar_wait(bar(TB_S_FULL + t), j & 1, ab, p.err, 901);
       if (!ok) break;

@@ -198,9 +198,9 @@ def qk_indexmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz=128):
 _scratch = {}
 
 
-def _block_scratch(q):
+def _block_scratch(q, k=None):
     B, H, S, _ = q.shape
-    need = cuda_attn.block_scratch_bytes(B, H, S, S)
+    need = cuda_attn.block_scratch_bytes(B, H, S, S if k is None else k.shape[2])
     per_head = need // (B * H)
     free, _total = torch.cuda.mem_get_info(q.device)
     heads_fit = max(1, min(B * H, int(free * 0.5) // per_head))     # fewer heads -> the op loops over chunks
@@ -215,14 +215,14 @@ def qk_block_indexmask_cuda(q, k, thresh, v=None):
     """64x64 block mode, one pass: returns (kb_indices [B,H,nqb,nkb], kb_counts [B,H,nqb], max_q,
     denom) and, when v is given, the dense attention output as a fifth element."""
     B, H, S, D = q.shape
-    nqb = nkb = (S + 63) // 64
+    nqb, nkb = (S + 63) // 64, (k.shape[2] + 63) // 64
     kb_indices = torch.empty((B, H, nqb, nkb), device=q.device, dtype=torch.int32)
     kb_counts = torch.empty((B, H, nqb), device=q.device, dtype=torch.int32)
     max_q = torch.empty((B, H, 1, _pad128(S)), dtype=torch.float32, device=q.device)
     denom = torch.empty_like(max_q)
     o = torch.empty((B, H, S, D), device=q.device, dtype=torch.bfloat16) if v is not None else None
     spattn_interface.block_index_lists(kb_indices, kb_counts, max_q, denom, o, q.contiguous(), k.contiguous(),
-                                       None if v is None else v.contiguous(), thresh, _block_scratch(q))
+                                       None if v is None else v.contiguous(), thresh, _block_scratch(q, k))
     return (kb_indices, kb_counts, max_q, denom) + ((o,) if v is not None else ())
 
 

@@ -9,7 +9,10 @@
  * Conventions (python/extension.cpp:52-73, python/spattn/sparseattn_functionals.py:10-26):
  *   q, k, v, o : bf16, [B, H, S, D] contiguous, 16-byte aligned, D in {64, 128}
  *   max_q, denom : fp32 [B, H, 1, S_pad], S_pad = ceil(S/128)*128; tail max = 0, tail denom = -inf
- *   kv_seq_len : number of leading key/value rows that take part (1..S); the reference hard-codes
+ *   seq        : query rows S; o, max_q, denom follow it
+ *   kv_rows    : rows per head of the k / v tensors ([B, H, kv_rows, D]); equal to seq in the reference,
+ *                free here (shorter or longer key / value sequences)
+ *   kv_seq_len : number of leading key/value rows that take part (1..kv_rows); the reference hard-codes
  *                this per shape (python/cuda_attn.cu:28-31), here it is a run-time argument
  *   scale      : softmax scale; pass 0 for 1/sqrt(D) (the reference hard-codes 1/sqrt(128),
  *                include/fullattn_tma.cuh:182-183)
@@ -48,19 +51,20 @@ int fgattn_check(void* stream, int* code);
  * Replaces attn_fwd_wg_impl (python/extension.cpp:4-7, python/cuda_attn.cu:9-38), i.e. the
  * full_attn operator (python/extension.cpp:52-73). */
 int fgattn_full_attn(void* o, const void* q, const void* k, const void* v, int batch, int heads, int seq, int D,
-                     int kv_seq_len, float scale, void* stream);
+                     int kv_rows, int kv_seq_len, float scale, void* stream);
 
 /* Dense attention that also emits the per-row raw maximum and softmax denominator.
  * Replaces attn_maxq_denom_impl (python/extension.cpp:22-27, python/cuda_attn.cu:97-139), the
  * fullattn_maxq_denom operator (python/extension.cpp:178-204). */
 int fgattn_fullattn_maxq_denom(void* o, float* max_q, float* denom, const void* q, const void* k, const void* v,
-                               int batch, int heads, int seq, int D, int kv_seq_len, float scale, void* stream);
+                               int batch, int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale,
+                               void* stream);
 
 /* Per-row raw maximum m_i = max_j q_i.k_j and denominator l_i = sum_j exp((q_i.k_j - m_i)*scale).
  * Replaces maxq_denom_impl (python/extension.cpp:29-33, python/cuda_attn.cu:142-180), the
  * maxq_denom operator (python/extension.cpp:226-248). */
 int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, int batch, int heads, int seq, int D,
-                      int kv_seq_len, float scale, void* stream);
+                      int kv_rows, int kv_seq_len, float scale, void* stream);
 
 /* Threshold mask at the reference granularity: booleanmask[b,h,qblk,j] (int32,
  * [B,H,ceil(S/128),mask_stride]) becomes 1 where some row of the 128-row query block has softmax
@@ -69,8 +73,8 @@ int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, 
  * Replaces booleanmask_128_impl (python/extension.cpp:36-41, python/cuda_attn.cu:183-266), the
  * booleanmask_128 operator (python/extension.cpp:271-297). */
 int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
-                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_seq_len,
-                           float scale, void* stream);
+                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_rows,
+                           int kv_seq_len, float scale, void* stream);
 
 /* Mask rows -> ascending index lists: for every (b,h,seqblock) row of booleanmask
  * ([B,H,seqblocks,mask_stride] int32, > 0 = keep) write the kept columns < seq in ascending order
@@ -91,8 +95,8 @@ int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int h
  * Replaces attn_sparse_fwd_wg_impl (python/extension.cpp:10-14, python/cuda_attn.cu:41-75), the
  * sp_attn operator (python/extension.cpp:125-154). */
 int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
-                   const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, float scale,
-                   void* stream);
+                   const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, int kv_rows,
+                   float scale, void* stream);
 
 /* ---- 64x64 block granularity --------------------------------------------------------------- */
 
@@ -110,8 +114,8 @@ size_t fgattn_block_scratch_bytes(int batch, int heads, int seq, int kv_seq_len)
  * granularity, without the second Q K^T pass of include/mask_utils.cuh:131-243. */
 int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, float* max_q, float* denom, void* o,
                              const void* q, const void* k, const void* v, float threshold, int batch, int heads,
-                             int seq, int D, int kv_seq_len, float scale, void* scratch, size_t scratch_bytes,
-                             void* stream);
+                             int seq, int D, int kv_rows, int kv_seq_len, float scale, void* scratch,
+                             size_t scratch_bytes, void* stream);
 
 /* Largest scratch the library itself can lend: see fgattn_block_index_lists_noalloc. */
 #define FGATTN_NOALLOC_SCRATCH_BYTES (64u << 20)
@@ -127,7 +131,8 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
  * exits).  One (batch, head) unit needs ceil(kv_seq_len/64) * ceil(seq/128)*128 * 4 bytes of it, so a
  * unit up to seq = kv_seq_len = 32768 fits; units are processed in as many head chunks as needed, and
  * a unit that does not fit returns FGATTN_SCRATCH_TOO_SMALL without launching anything.
- * Same arguments and results as fgattn_block_index_lists, minus the scratch pointer.  It calls no
+ * Same arguments and results as fgattn_block_index_lists, minus the scratch pointer and with
+ * kv_rows = seq (k / v as long as q).  It calls no
  * cudaMalloc / cudaFree and no allocating library routine; bounded-wait time-outs go to the error
  * word that fgattn_check reads if some earlier call created it, else to a word inside the library.
  * The first call on a device looks up the device address of the built-in array (once per device,
@@ -147,7 +152,7 @@ int fgattn_block_index_lists_noalloc(int* kb_indices, int* kb_counts, int list_s
  * of the persistent kernel. */
 int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                              const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
-                             int heads, int seq, int D, int kv_seq_len, float scale, void* workspace,
+                             int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream);
 
 /* Bytes of device workspace fgattn_sp_attn_blocks_ml needs (work-queue counter + per-head processing
@@ -158,8 +163,8 @@ size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);
 /* Same gather kernel with the renormalising softmax of the sp_attn operator (softmax over the kept
  * keys only, include/sparseattn_asyncgatherload_padded.cuh:198-249) on key-block lists. */
 int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
-                          const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_seq_len,
-                          float scale, void* stream);
+                          const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_rows,
+                          int kv_seq_len, float scale, void* stream);
 
 /* ---- one-bit-per-entry masks (mask caches) ---------------------------------------------------
  * Entry e of a row lives in byte e / 8, bit e % 8 (least significant bit first): the format of pack /
@@ -191,7 +196,7 @@ int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, co
 /* ---- top-k selector ------------------------------------------------------------------------- */
 
 /* Bytes of scratch fgattn_topk_indices needs (block means as two bf16 tensors + the fp32 score rows). */
-size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz);
+size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz, int kv_seq_len);
 
 /* Alternative list producer: for every block of `blocksz` query rows (the last block may be shorter)
  * score(key) = mean of the block's query rows . key * scale, and the select_k keys < kv_seq_len with the
@@ -201,8 +206,8 @@ size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int block
  * rounds block means and scores to bf16, which makes its order among near-equal scores arbitrary).
  * select_k <= 8192.  Replaces qk_topkmask_indices (python/spattn/mask_utils.py:389-417). */
 int fgattn_topk_indices(int* kv_indices, int* kv_num_indices, int list_stride, const void* q, const void* k,
-                        int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_seq_len, float scale,
-                        void* scratch, size_t scratch_bytes, void* stream);
+                        int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_rows, int kv_seq_len,
+                        float scale, void* scratch, size_t scratch_bytes, void* stream);
 
 #ifdef __cplusplus
 }

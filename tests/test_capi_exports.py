@@ -43,13 +43,14 @@ def test_argument_validation_needs_no_device():
     lib = capi.lib()
     null = ctypes.c_void_p(0)
     buf = ctypes.c_void_p(0x1000)
-    assert lib.fgattn_full_attn(null, buf, buf, buf, 1, 1, 64, 64, 64, 0.0, null) == 1      # null output
-    assert lib.fgattn_full_attn(buf, buf, buf, buf, 1, 1, 64, 96, 64, 0.0, null) == 2       # head dim
-    assert lib.fgattn_full_attn(buf, buf, buf, buf, 1, 1, 64, 64, 65, 0.0, null) == 1       # kv_seq_len > S
-    assert lib.fgattn_full_attn(buf, ctypes.c_void_p(0x1008), buf, buf, 1, 1, 64, 64, 64, 0.0, null) == 3
-    assert lib.fgattn_maxq_denom(null, null, buf, buf, 1, 1, 64, 64, 64, 0.0, null) == 1
+    assert lib.fgattn_full_attn(null, buf, buf, buf, 1, 1, 64, 64, 64, 64, 0.0, null) == 1  # null output
+    assert lib.fgattn_full_attn(buf, buf, buf, buf, 1, 1, 64, 96, 64, 64, 0.0, null) == 2   # head dim
+    assert lib.fgattn_full_attn(buf, buf, buf, buf, 1, 1, 64, 64, 64, 65, 0.0, null) == 1   # kv_seq_len > kv_rows
+    assert lib.fgattn_full_attn(buf, buf, buf, buf, 1, 1, 64, 64, 0, 0, 0.0, null) == 1     # no key rows
+    assert lib.fgattn_full_attn(buf, ctypes.c_void_p(0x1008), buf, buf, 1, 1, 64, 64, 64, 64, 0.0, null) == 3
+    assert lib.fgattn_maxq_denom(null, null, buf, buf, 1, 1, 64, 64, 64, 64, 0.0, null) == 1
     assert lib.fgattn_booleanmask_to_indexmask(buf, buf, buf, 1, 1, 64, 0, 128, null) == 1
-    assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 0.0, buf, 64, null) == 1
+    assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 64, 0.0, buf, 64, null) == 1
     # one-bit-per-entry masks
     assert lib.fgattn_pack_mask(null, buf, 4, 8, 64, null) == 1                             # null output
     assert lib.fgattn_pack_mask(buf, buf, 2, 8, 64, null) == 2                              # element size
@@ -59,10 +60,10 @@ def test_argument_validation_needs_no_device():
     assert lib.fgattn_packedmask_to_indexmask(buf, buf, buf, 8, 64, 0, 64, 64, null) == 1   # list stride
     assert lib.fgattn_indexmask_to_packedmask(buf, buf, buf, 8, 64, 8 * 64 * 1024, null) == 2   # row too wide
     # top-k selector
-    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 0, 1, 1, 256, 64, 128, 256, 0.0, buf, 1 << 30, null) == 1
-    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 129, 1, 1, 256, 64, 128, 256, 0.0, buf, 1 << 30, null) == 1
-    assert lib.fgattn_topk_indices(buf, buf, 16384, buf, buf, 9000, 1, 1, 16384, 64, 128, 16384, 0.0, buf, 1 << 40, null) == 2
-    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 64, 1, 1, 256, 64, 128, 256, 0.0, buf, 16, null) == 7
+    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 0, 1, 1, 256, 64, 128, 256, 256, 0.0, buf, 1 << 30, null) == 1
+    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 129, 1, 1, 256, 64, 128, 256, 256, 0.0, buf, 1 << 30, null) == 1
+    assert lib.fgattn_topk_indices(buf, buf, 16384, buf, buf, 9000, 1, 1, 16384, 64, 128, 16384, 16384, 0.0, buf, 1 << 40, null) == 2
+    assert lib.fgattn_topk_indices(buf, buf, 128, buf, buf, 64, 1, 1, 256, 64, 128, 256, 256, 0.0, buf, 16, null) == 7
     assert capi.topk_scratch_bytes(1, 12, 32760, 128, 128) == 2 * 12 * 256 * 128 * 2 + 12 * 256 * 32768 * 4
 
 
