@@ -301,12 +301,8 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
   p.scale_log2 = resolve_scale_log2(scale, D);
   r = get_err_word(&p.err);
   if (r) return r;
-  // k / v as row matrices for the four-row gather: the row coordinate is 32 bits
-  const long long kv_total_rows = (long long)batch * heads * kv_rows;
-  if (kv_total_rows > 2147483647LL) return FGATTN_UNSUPPORTED;
-  CUtensorMap mq, mkr, mvr;
-  if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128) || fg::make_rows_map(&mkr, k, kv_total_rows, D) ||
-      fg::make_rows_map(&mvr, v, kv_total_rows, D))
+  CUtensorMap mq;
+  if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   dim3 grid((seq + 255) / 256, batch * heads, 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -314,12 +310,12 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
     auto kern = fg::sparse_token_attn_kernel<128>;
     r = set_smem(kern, fg::TokenCfg<128>::kSmemBytes);
     if (r) return r;
-    kern<<<grid, 384, fg::TokenCfg<128>::kSmemBytes, st>>>(mq, mkr, mvr, p);
+    kern<<<grid, 384, fg::TokenCfg<128>::kSmemBytes, st>>>(mq, p);
   } else {
     auto kern = fg::sparse_token_attn_kernel<64>;
     r = set_smem(kern, fg::TokenCfg<64>::kSmemBytes);
     if (r) return r;
-    kern<<<grid, 384, fg::TokenCfg<64>::kSmemBytes, st>>>(mq, mkr, mvr, p);
+    kern<<<grid, 384, fg::TokenCfg<64>::kSmemBytes, st>>>(mq, p);
   }
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;

@@ -173,16 +173,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
-// Four arbitrary rows of a 2-D tensor (box = one row of the map's inner extent) into four consecutive
-// shared-memory rows: {col, row0, row1, row2, row3}.  The barrier receives 4 x box bytes.
-__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int col, int r0, int r1,
-                                               int r2, int r3) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
-      "%6, %7}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2,
                                             int c3) {
   asm volatile(

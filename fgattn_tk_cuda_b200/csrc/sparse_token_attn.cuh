@@ -1,9 +1,7 @@
 // Sparse attention over key-TOKEN lists at the reference granularity (128-row query blocks).
 // For each query block the listed K/V rows are gathered 128 at a time into swizzled shared-memory
-// tiles by the TMA four-row gather (tile::gather4: one instruction fetches four arbitrary rows of a
-// 64-column half into four consecutive tile rows, so a lane issues two instructions per tile and one
-// warp feeds the whole ring), and the flash-attention step over the gathered keys runs on tcgen05 with
-// an online (renormalising) softmax.  A CTA runs two query
+// tiles (16-byte cp.async per chunk, whole rows per warp-wide copy, three gather warps), and the flash-attention step over the
+// gathered keys runs on tcgen05 with an online (renormalising) softmax.  A CTA runs two query
 // blocks ("slots") against one tensor pipe; their K/V tiles share one ring in consumption order.
 // List entries >= the number of key rows, and slots past the count, are masked out.
 #pragma once
@@ -28,6 +26,7 @@ struct TokenCfg {
   static constexpr int kHalves = D / 64;
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kGatherThreads = 96;
   static constexpr int kOffQ = 0;
   static constexpr int kOffRing = 2 * kTileBytes;
   static constexpr int kOffBar = kOffRing + kStages * kTileBytes;
@@ -36,10 +35,16 @@ struct TokenCfg {
 
 enum : int { TB_Q_FULL = 0, TB_FULL = 1, TB_EMPTY = 9, TB_S_FULL = 17, TB_P_FULL = 19, TB_O_FULL = 21, TB_COUNT = 23 };
 
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int D>
 __global__ void __launch_bounds__(384, 1)
-sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mkr,
-                         const __grid_constant__ CUtensorMap mvr, const TokenParams p) {
+sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenParams p) {
   using Cfg = TokenCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -57,7 +62,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
     ab->flag = 0;
     mbar_init(bar(TB_Q_FULL), 1);
     for (int s = 0; s < 8; ++s) {
-      mbar_init(bar(TB_FULL + s), 1);
+      mbar_init(bar(TB_FULL + s), Cfg::kGatherThreads);
       mbar_init(bar(TB_EMPTY + s), 1);
     }
     for (int t = 0; t < 2; ++t) {
@@ -105,50 +110,70 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
                       bh);
     }
     __syncwarp();
-    if (warp == 8) {
-      // mkr / mvr see k / v as matrices of B*H*S_kv rows; a lane owns tile rows 4*lane .. 4*lane+3
-      tma_prefetch_desc(&mkr);
-      tma_prefetch_desc(&mvr);
-      const int row_base = bh * p.S_kv;
-      int idx = 0;
-      bool ok = true;
-      auto gather_tile = [&](const CUtensorMap* m, int t, int j) {
-        const int st = idx % Cfg::kStages, f = idx / Cfg::kStages;
-        int r[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int pos = j * 128 + 4 * lane + i;
-          int tok = (pos < cnt[t]) ? lst[t][pos] : 0;
-          if (tok < 0 || tok >= p.S_kv) tok = 0;                       // masked column: any finite row will do
-          r[i] = row_base + tok;
-        }
-        if (f > 0) ok = mbar_wait_warp(bar(TB_EMPTY + st), (f - 1) & 1, ab, p.err, 701);
-        if (!ok) return;
-        const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes + lane * 512;
-        if (lane == 0) mbar_arrive_expect_tx(bar(TB_FULL + st), Cfg::kTileBytes);
-        __syncwarp();
-#pragma unroll
-        for (int h = 0; h < Cfg::kHalves; ++h)
-          tma_gather4_2d(dst + h * 16384, m, bar(TB_FULL + st), h * 64, r[0], r[1], r[2], r[3]);
-        ++idx;
-      };
-      // order: K(0,0) K(1,0), then per step V(t,j) K(t,j+1)
-      if (nst[0] > 0) gather_tile(&mkr, 0, 0);
-      if (nst[1] > 0 && ok) gather_tile(&mkr, 1, 0);
-      for (int j = 0; j < n_max && ok; ++j) {
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j < nst[t]) {
-            gather_tile(&mvr, t, j);
-            if (ok && j + 1 < nst[t]) gather_tile(&mkr, t, j + 1);
+    const int gw = (warp == 8) ? 0 : warp - 9;                         // gather warp 0..2
+    constexpr int kChunksPerRow = D / 8;                               // 16-byte chunks per row
+    constexpr int kRowsPerInstr = 32 / kChunksPerRow;                  // rows one warp-wide copy covers
+    // rows of a 128-token tile are dealt to the three gather warps in contiguous runs of 44 / 44 / 40;
+    // a lane keeps the token ids of run rows `lane` and `lane + 32`
+    const int row0 = gw * 44, nrows = (gw == 2) ? 40 : 44;
+    const int sub = lane / kChunksPerRow, ch = lane % kChunksPerRow;
+    int idx = 0;
+    bool ok = true;
+    int pending_stage = -1;                                            // tile whose copies are in flight
+    int tokA[2] = {0, 0}, tokB[2] = {0, 0};                            // token ids of the slot's current step
+    auto load_tokens = [&](int t, int j) {
+      const int pa = j * 128 + row0 + lane, pb = pa + 32;
+      int a = (pa < cnt[t]) ? lst[t][pa] : 0;
+      int b = (lane + 32 < nrows && pb < cnt[t]) ? lst[t][pb] : 0;
+      if (a < 0 || a >= p.S_kv) a = 0;                                    // masked column: any finite row will do
+      if (b < 0 || b >= p.S_kv) b = 0;
+      tokA[t] = a;
+      tokB[t] = b;
+    };
+    // Each copy instruction moves whole rows: 16 (D = 128) or 8 (D = 64) neighbouring lanes fetch the
+    // consecutive 16-byte chunks of one row, so a warp-wide copy asks L2 for full 128-byte lines
+    // instead of 32 separate sectors.
+    auto gather_tile = [&](const __nv_bfloat16* base, int t) {
+      const int st = idx % Cfg::kStages, f = idx / Cfg::kStages;
+      if (f > 0) ok = mbar_wait(bar(TB_EMPTY + st), (f - 1) & 1, ab, p.err, 701);
+      if (!ok) return;
+      const uint32_t dst = sbase + Cfg::kOffRing + st * Cfg::kTileBytes + (ch >> 3) * 16384;
+      const __nv_bfloat16* src0 = base + size_t(bh) * p.S_kv * D + ch * 8;
+      for (int r = 0; r < nrows; r += kRowsPerInstr) {                 // nrows is a multiple of 4
+        const int lr = r + sub;                                        // run row of this lane
+        const int ta = __shfl_sync(0xffffffffu, tokA[t], lr & 31), tb = __shfl_sync(0xffffffffu, tokB[t], lr & 31);
+        const int tok = (lr < 32) ? ta : tb;
+        cp_async_16(dst + sw128_offset(row0 + lr, ch & 7), src0 + size_t(tok) * D);
+      }
+      cp_async_commit();
+      if (pending_stage >= 0) {
+        cp_async_wait<1>();                                            // the previous tile has landed
+        fence_proxy_async_smem();
+        mbar_arrive(bar(TB_FULL + pending_stage));
+      }
+      pending_stage = st;
+      ++idx;
+    };
+    // order: K(0,0) K(1,0), then per step V(t,j) K(t,j+1); the ids of step j serve K(t,j) and V(t,j)
+    if (nst[0] > 0) { load_tokens(0, 0); gather_tile(p.k, 0); }
+    if (nst[1] > 0 && ok) { load_tokens(1, 0); gather_tile(p.k, 1); }
+    for (int j = 0; j < n_max && ok; ++j) {
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (j < nst[t]) {
+          gather_tile(p.v, t);
+          if (ok && j + 1 < nst[t]) {
+            load_tokens(t, j + 1);
+            gather_tile(p.k, t);
           }
         }
       }
-      if (!ok) {                                                       // let copies in flight land before leaving
-        for (int i = max(0, idx - Cfg::kStages); i < idx; ++i)
-          mbar_wait_brief(bar(TB_FULL + i % Cfg::kStages), (i / Cfg::kStages) & 1);
-        if (lane == 0) mbar_wait_brief(bar(TB_Q_FULL), 0);
-      }
     }
+    cp_async_wait<0>();
+    if (ok && pending_stage >= 0) {
+      fence_proxy_async_smem();
+      mbar_arrive(bar(TB_FULL + pending_stage));
+    }
+    if (!ok && warp == 8 && lane == 0) mbar_wait_brief(bar(TB_Q_FULL), 0);
   } else if (warp == 9) {
     // ------------------------------------------------------------------ UMMA issuer
     reg_dealloc<72>();

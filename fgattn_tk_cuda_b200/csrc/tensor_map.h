@@ -42,20 +42,4 @@ inline int make_qkv_map(CUtensorMap* map, const void* base, int heads, int rows,
   return r == CUDA_SUCCESS ? 0 : 2;
 }
 
-// bf16 matrix [rows, D] (contiguous) as a 2-D map (D, rows) with a (64 elements, 1 row) box and the
-// 128-byte swizzle: the form the four-row gather (tile::gather4) takes, which moves four such boxes
-// per instruction.  Returns 0 on success.
-inline int make_rows_map(CUtensorMap* map, const void* base, long long rows, int D) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return 1;
-  cuuint64_t dims[2] = {cuuint64_t(D), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(D) * 2};
-  cuuint32_t box[2] = {64, 1};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 2;
-}
-
 }  // namespace fg
