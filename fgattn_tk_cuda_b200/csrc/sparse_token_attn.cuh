@@ -235,15 +235,20 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
     OnlineState st;
     online_init(st);
     bool ok = true;
-    for (int j = 0; j < nst[t]; ++j) {
-      // which of the step's 128 gathered columns are real keys
-      uint32_t live[4];
+    // which of a step's 128 gathered columns are real keys; fetched one step ahead so that the list
+    // loads overlap the products of the current step instead of opening every step with a global-memory
+    // round trip
+    uint32_t live[4];
+    auto fetch_live = [&](int j) {
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const int pos = j * 128 + w * 32 + lane;
-        const int tok = (pos < cnt[t]) ? lst[t][pos] : -1;
+        const int tok = (j < nst[t] && pos < cnt[t]) ? lst[t][pos] : -1;
         live[w] = __ballot_sync(0xffffffffu, tok >= 0 && tok < p.S_kv);
       }
+    };
+    fetch_live(0);
+    for (int j = 0; j < nst[t]; ++j) {
       ok = mbar_wait(bar(TB_S_FULL + t), j & 1, ab, p.err, 901);
       if (!ok) break;
       tc_fence_after();
@@ -251,6 +256,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       softmax_online_step<D, true>(s_addr, s_addr, o_addr, 64, 64, p.scale_log2, j == 0, st, mx0, mx1, live);
       tc_fence_before();
       mbar_arrive(bar(TB_P_FULL + t));
+      fetch_live(j + 1);
     }
     __nv_bfloat16* orow = p.o + (size_t(bh) * p.S + row) * D;
     if (nst[t] == 0) {
