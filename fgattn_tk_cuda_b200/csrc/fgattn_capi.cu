@@ -114,20 +114,16 @@ int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int 
   return get_err_word(&s.p.err);
 }
 
-template <bool RENORM>
+// Renormalising block-sparse attention (two-slot kernel).
 int launch_sparse(void* o, const void* q, const void* k, const void* v, const int* kb_idx, const int* kb_cnt,
-                  int list_stride, const float* max_q, const float* denom, int B, int H, int S, int D, int kv_rows,
-                  int kv_len, float scale, cudaStream_t st) {
+                  int list_stride, int B, int H, int S, int D, int kv_rows, int kv_len, float scale, cudaStream_t st) {
   int r = check_qk(q, k, B, H, S, D, kv_rows, kv_len);
   if (r) return r;
   if (!o || !v || !kb_idx || !kb_cnt) return FGATTN_INVALID_ARGUMENT;
-  if (!RENORM && (!max_q || !denom)) return FGATTN_INVALID_ARGUMENT;
   if (!aligned16(o) || !aligned16(v)) return FGATTN_MISALIGNED;
   fg::SparseParams p;
   memset(&p, 0, sizeof(p));
   p.o = static_cast<__nv_bfloat16*>(o);
-  p.max_q = max_q;
-  p.denom = denom;
   p.kb_idx = kb_idx;
   p.kb_cnt = kb_cnt;
   p.S = S;
@@ -149,14 +145,14 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
   if (D == 128) {
     const int smem = fg::SparseCfg<128>::smem_bytes(p.list_cap, p.nkb);
     if (smem > 232448) return FGATTN_UNSUPPORTED;
-    auto kern = fg::sparse_block_attn_kernel<128, RENORM>;
+    auto kern = fg::sparse_block_attn_kernel<128>;
     r = set_smem(kern, smem);
     if (r) return r;
     kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
   } else {
     const int smem = fg::SparseCfg<64>::smem_bytes(p.list_cap, p.nkb);
     if (smem > 232448) return FGATTN_UNSUPPORTED;
-    auto kern = fg::sparse_block_attn_kernel<64, RENORM>;
+    auto kern = fg::sparse_block_attn_kernel<64>;
     r = set_smem(kern, smem);
     if (r) return r;
     kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
@@ -593,8 +589,8 @@ int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, co
 int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                           const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_rows,
                           int kv_seq_len, float scale, void* stream) {
-  return launch_sparse<true>(o, q, k, v, kb_indices, kb_counts, list_stride, nullptr, nullptr, batch, heads, seq, D,
-                             kv_rows, kv_seq_len, scale, static_cast<cudaStream_t>(stream));
+  return launch_sparse(o, q, k, v, kb_indices, kb_counts, list_stride, batch, heads, seq, D, kv_rows, kv_seq_len, scale,
+                       static_cast<cudaStream_t>(stream));
 }
 
 // ---- top-k selector ------------------------------------------------------------------------------

@@ -61,29 +61,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-#ifdef FG_SPIN_TEST_WAIT
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "selp.b32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds and
-// wakes as soon as the phase completes, so a waiting warp does not burn issue slots of the
-// sub-partition it shares with the math warps.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
@@ -144,14 +125,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ab
   return __all_sync(0xffffffffu, ok);
 }
 
-// Converged-warp wait where only lane 0 polls the barrier; the other lanes park at the shuffle.
-// Keeps the number of threads hammering shared memory with try_wait small.
-__device__ __forceinline__ bool mbar_wait_leader(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ab, err, code) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
 // Wait used only on the abort path: short budget, no error recording.
 __device__ __forceinline__ void mbar_wait_brief(uint32_t bar, uint32_t parity) {
   long long t0 = clock64();
@@ -171,13 +144,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2,
-                                            int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 
@@ -337,34 +303,6 @@ __device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-
-// 2^x for two values on the FMA pipe (no MUFU): round-to-nearest split x = n + f, f in [-0.5, 0.5],
-// cubic minimax polynomial for 2^f (max relative error 7.5e-5, far below bf16 resolution), n added
-// to the exponent field.  Inputs below -126 give ~1e-38.
-__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& p0, float& p1) {
-  const float kMagic = 12582912.0f;                       // 1.5 * 2^23
-  x0 = fmaxf(x0, -126.0f);
-  x1 = fmaxf(x1, -126.0f);
-  const uint64_t x = f2_pack(x0, x1);
-  const uint64_t xr = f2_add(x, f2_pack(kMagic, kMagic));  // integer part in the low mantissa bits
-  const uint64_t xi = f2_add(xr, f2_pack(-kMagic, -kMagic));
-  const uint64_t f = f2_fma(xi, f2_pack(-1.0f, -1.0f), x);
-  uint64_t q = f2_fma(f, f2_pack(0.05517160892486572f, 0.05517160892486572f),
-                      f2_pack(0.2426111102104187f, 0.2426111102104187f));
-  q = f2_fma(q, f, f2_pack(0.6932609677314758f, 0.6932609677314758f));
-  q = f2_fma(q, f, f2_pack(0.9999280571937561f, 0.9999280571937561f));
-  float q0, q1, r0, r1;
-  f2_unpack(q, q0, q1);
-  f2_unpack(xr, r0, r1);
-  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
-  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
-}
-
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -4,10 +4,6 @@
 #pragma once
 #include "sm100_ptx.cuh"
 
-#ifndef FG_DENSE_POLY_OF8
-#define FG_DENSE_POLY_OF8 0      // of every 8 column pairs, how many use the polynomial exp2
-#endif
-
 namespace fg {
 
 struct OnlineState {
@@ -24,15 +20,6 @@ __device__ __forceinline__ void online_init(OnlineState& st) {
   st.m_used = -1.0e30f;
   st.m_true = -INFINITY;
   st.l = 0.f;
-}
-
-template <int N>
-__device__ __forceinline__ void mask_cols(uint32_t (&r)[N], int valid) {
-  if (valid < N) {
-#pragma unroll
-    for (int i = 0; i < N; ++i)
-      if (i >= valid) r[i] = __float_as_uint(-INFINITY);
-  }
 }
 
 // Online softmax over one score tile.
@@ -118,13 +105,8 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
     }
 #pragma unroll
     for (int i = w * 32; i < w * 32 + 32; i += 2) {
-      float p0, p1;
-      if (((i >> 1) & 7) < FG_DENSE_POLY_OF8) {      // part of the exponentials on the FMA pipe
-        ex2_poly2(fmaf(__uint_as_float(r[i]), c, neg_m), fmaf(__uint_as_float(r[i + 1]), c, neg_m), p0, p1);
-      } else {
-        p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
-        p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
-      }
+      const float p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
+      const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
       sum0 += p0;
       sum1 += p1;
       if (WRITE_P) r[i >> 1] = pack_bf16(p0, p1);
@@ -136,38 +118,6 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
     for (int cc = 0; cc < 4; ++cc) tmem_st16(p_addr + cc * 16, *reinterpret_cast<uint32_t(*)[16]>(&r[cc * 16]));
     tmem_st_wait();
   }
-}
-
-// Probabilities from a precomputed log-sum-exp: p = 2^(s*c - t_row), t_row = m*c + log2(l).
-// No reductions.  A half with valid == 0 is not even read; its probabilities are zero.
-__device__ __forceinline__ void softmax_ml_step(uint32_t s_addr, uint32_t p_addr, int valid0, int valid1, float c,
-                                                float t_row) {
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int valid = half ? valid1 : valid0;
-    uint32_t pk[32];
-    if (valid > 0) {                                   // warp-uniform
-      uint32_t r[64];
-      tmem_ld32(s_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-      tmem_ld32(s_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 64; i += 2) {
-        float p0 = ex2(fmaf(__uint_as_float(r[i]), c, -t_row));
-        float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, -t_row));
-        if (valid < 64) {
-          if (i >= valid) p0 = 0.f;
-          if (i + 1 >= valid) p1 = 0.f;
-        }
-        pk[i >> 1] = pack_bf16(p0, p1);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) pk[i] = 0u;
-    }
-    tmem_st32(p_addr + half * 32, pk);
-  }
-  tmem_st_wait();
 }
 
 // Write one row of the fp32 accumulator (D columns at o_addr) as bf16, scaled by `inv`.

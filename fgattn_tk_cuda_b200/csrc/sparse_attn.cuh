@@ -8,9 +8,9 @@
 // q0 .. q0+255) that feed one tensor pipe alternately; K/V tiles go through one shared ring in the
 // exact order the UMMA issuer consumes them.
 //
-// ML mode   : probabilities use the precomputed per-row max m and denominator l of the softmax over
-//             ALL keys (no renormalisation) -- the masked attention of the PyTorch reference.
-// RENORM    : online softmax over the kept keys only -- what the sp_attn operator computes.
+// The softmax is the online (renormalising) one over the kept keys only, what the sp_attn operator
+// computes: one thread owns a whole query row of a slot, so the running maximum stays in its
+// registers.  (The form with precomputed max_q / denom lives in sparse_ml_persistent.cuh.)
 #pragma once
 #include "sm100_ptx.cuh"
 #include "softmax_steps.cuh"
@@ -19,8 +19,6 @@ namespace fg {
 
 struct SparseParams {
   __nv_bfloat16* o;          // [BH, S, D]
-  const float* max_q;        // [BH, S_pad]  (ML mode)
-  const float* denom;        // [BH, S_pad]
   const int* kb_idx;         // [BH, nqb, list_stride] ascending key-block indices
   const int* kb_cnt;         // [BH, nqb]
   int* err;
@@ -56,7 +54,7 @@ enum : int {
 // entry = key block index | (kept by rows 0-63) << 30 | (kept by rows 64-127) << 31
 __device__ __forceinline__ int entry_kb(uint32_t e) { return int(e & 0x3FFFFFFFu); }
 
-template <int D, bool RENORM>
+template <int D>
 __global__ void __launch_bounds__(384, 1)
 sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                          const __grid_constant__ CUtensorMap mv, const SparseParams p) {
@@ -261,15 +259,8 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
     const float c = p.scale_log2;
     const int nt = t ? n1 : n0;
     const uint32_t* list = lists + t * p.list_cap;
-    float t_row = INFINITY;
     OnlineState st;
     online_init(st);
-    if (!RENORM) {
-      if (row < p.S) {
-        const size_t off = size_t(bh) * p.S_pad + row;
-        t_row = p.max_q[off] * c + log2f(p.denom[off]);
-      }
-    }
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
       const uint32_t e0 = list[2 * j], e1 = list[2 * j + 1];
@@ -278,12 +269,8 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
       ok = mbar_wait(bar(SB_S_FULL + t), j & 1, ab, p.err, 601);
       if (!ok) break;
       tc_fence_after();
-      if (RENORM) {
-        float mx0, mx1;
-        softmax_online_step<D, true>(s_addr, s_addr, o_addr, valid0, valid1, c, j == 0, st, mx0, mx1);
-      } else {
-        softmax_ml_step(s_addr, s_addr, valid0, valid1, c, t_row);
-      }
+      float mx0, mx1;
+      softmax_online_step<D, true>(s_addr, s_addr, o_addr, valid0, valid1, c, j == 0, st, mx0, mx1);
       tc_fence_before();
       mbar_arrive(bar(SB_P_FULL + t));
     }
@@ -297,7 +284,7 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
       ok = mbar_wait(bar(SB_O_FULL + t), 0, ab, p.err, 602);
       if (ok) {
         tc_fence_after();
-        const float inv = RENORM ? (st.l > 0.f ? 1.0f / st.l : 0.f) : 1.0f;
+        const float inv = st.l > 0.f ? 1.0f / st.l : 0.f;
         store_o_row<D>(o_addr, orow, inv, row < p.S);
       }
     }

@@ -29,9 +29,6 @@
 #include "softmax_steps.cuh"
 #include "sparse_attn.cuh"
 
-#ifndef FG_POLY_OF8
-#define FG_POLY_OF8 0
-#endif
 
 namespace fg {
 
@@ -103,25 +100,15 @@ struct ItemInfo {
 };
 
 // N score columns -> N/2 packed bf16 probability columns, p = 2^(s*c - t_row).
-// kPolyOf8 of every 8 column pairs go through the FMA-pipe polynomial, the rest through MUFU.
-template <int kPolyOf8, int N>
+template <int N>
 __device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[N / 2], int valid, float c,
                                          float t_row) {
   const uint64_t c2 = f2_pack(c, c), nt2 = f2_pack(-t_row, -t_row);
 #pragma unroll
   for (int i = 0; i < N; i += 2) {
-    float x0, x1, p0, p1;
+    float x0, x1;
     f2_unpack(f2_fma(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, nt2), x0, x1);
-#ifdef FG_NO_EX2
-    p0 = x0; p1 = x1;
-#else
-    if (((i >> 1) & 7) < kPolyOf8) {
-      ex2_poly2(x0, x1, p0, p1);
-    } else {
-      p0 = ex2(x0);
-      p1 = ex2(x1);
-    }
-#endif
+    float p0 = ex2(x0), p1 = ex2(x1);
     if (valid < N) {
       if (i >= valid) p0 = 0.f;
       if (i + 1 >= valid) p1 = 0.f;
@@ -546,7 +533,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
               uint32_t r[32];
               tmem_ld32(a + ch * 32, r);
               tmem_ld_wait();
-              ml_probs<FG_POLY_OF8, 32>(r, pk, valid, c, t_row);
+              ml_probs<32>(r, pk, valid, c, t_row);
             } else {
 #pragma unroll
               for (int i = 0; i < 16; ++i) pk[i] = 0u;
