@@ -306,12 +306,12 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
     auto kern = fg::sparse_token_attn_kernel<128>;
     r = set_smem(kern, fg::TokenCfg<128>::kSmemBytes);
     if (r) return r;
-    kern<<<grid, 384, fg::TokenCfg<128>::kSmemBytes, st>>>(mq, p);
+    kern<<<grid, fg::TokenCfg<128>::kThreads, fg::TokenCfg<128>::kSmemBytes, st>>>(mq, p);
   } else {
     auto kern = fg::sparse_token_attn_kernel<64>;
     r = set_smem(kern, fg::TokenCfg<64>::kSmemBytes);
     if (r) return r;
-    kern<<<grid, 384, fg::TokenCfg<64>::kSmemBytes, st>>>(mq, p);
+    kern<<<grid, fg::TokenCfg<64>::kThreads, fg::TokenCfg<64>::kSmemBytes, st>>>(mq, p);
   }
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;

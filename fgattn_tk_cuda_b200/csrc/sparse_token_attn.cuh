@@ -1,6 +1,6 @@
 // Sparse attention over key-TOKEN lists at the reference granularity (128-row query blocks).
 // For each query block the listed K/V rows are gathered 128 at a time into swizzled shared-memory
-// tiles (16-byte cp.async per chunk, whole rows per warp-wide copy, three gather warps), and the flash-attention step over the
+// tiles (16-byte cp.async per chunk, whole rows per warp-wide copy, seven gather warps), and the flash-attention step over the
 // gathered keys runs on tcgen05 with an online (renormalising) softmax.  A CTA runs two query
 // blocks ("slots") against one tensor pipe; their K/V tiles share one ring in consumption order.
 // List entries >= the number of key rows, and slots past the count, are masked out.
@@ -26,7 +26,9 @@ struct TokenCfg {
   static constexpr int kHalves = D / 64;
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kStages = (D == 128) ? 4 : 8;
-  static constexpr int kGatherThreads = 96;
+  static constexpr int kGatherWarps = 7;                  // the copies a warp can keep in flight are the limit
+  static constexpr int kGatherThreads = 32 * kGatherWarps;
+  static constexpr int kThreads = 32 * (8 + 1 + kGatherWarps);   // 8 softmax warps, the UMMA issuer, the gather warps
   static constexpr int kOffQ = 0;
   static constexpr int kOffRing = 2 * kTileBytes;
   static constexpr int kOffBar = kOffRing + kStages * kTileBytes;
@@ -43,7 +45,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(TokenCfg<D>::kThreads, 1)
 sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenParams p) {
   using Cfg = TokenCfg<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -100,7 +102,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
 
   if (warp == 8 || warp >= 10) {
     // ------------------------------------------------------------------ gather producers
-    reg_dealloc<72>();
+    reg_dealloc<48>();
     if (warp == 8 && lane == 0) {
       tma_prefetch_desc(&mq);
       mbar_arrive_expect_tx(bar(TB_Q_FULL), 2 * Cfg::kTileBytes);
@@ -110,12 +112,12 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
                       bh);
     }
     __syncwarp();
-    const int gw = (warp == 8) ? 0 : warp - 9;                         // gather warp 0..2
+    const int gw = (warp == 8) ? 0 : warp - 9;                         // gather warp 0..6
     constexpr int kChunksPerRow = D / 8;                               // 16-byte chunks per row
     constexpr int kRowsPerInstr = 32 / kChunksPerRow;                  // rows one warp-wide copy covers
-    // rows of a 128-token tile are dealt to the three gather warps in contiguous runs of 44 / 44 / 40;
-    // a lane keeps the token ids of run rows `lane` and `lane + 32`
-    const int row0 = gw * 44, nrows = (gw == 2) ? 40 : 44;
+    // rows of a 128-token tile are dealt to the seven gather warps in contiguous runs of 4 x 20 + 3 x 16;
+    // a lane keeps the token id of run row `lane` (and of `lane + 32` for runs longer than a warp)
+    const int row0 = (gw < 4) ? gw * 20 : 80 + (gw - 4) * 16, nrows = (gw < 4) ? 20 : 16;
     const int sub = lane / kChunksPerRow, ch = lane % kChunksPerRow;
     int idx = 0;
     bool ok = true;
@@ -176,7 +178,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
     if (!ok && warp == 8 && lane == 0) mbar_wait_brief(bar(TB_Q_FULL), 0);
   } else if (warp == 9) {
     // ------------------------------------------------------------------ UMMA issuer
-    reg_dealloc<72>();
+    reg_dealloc<48>();
     {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
@@ -227,7 +229,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    reg_alloc<216>();
+    reg_alloc<208>();
     const int t = warp >> 2, wq = warp & 3;
     const int row = q0 + t * 128 + wq * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
