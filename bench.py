@@ -252,6 +252,9 @@ def main():
     kidx = torch.empty(B, H, (S + 127) // 128, kstride, dtype=torch.int32, device=dev)
     tk_scratch = torch.empty(capi.topk_scratch_bytes(B, H, S, D, 128), dtype=torch.uint8, device=dev)
     ms_topk = ev_time(lambda: capi.topk_indices(kidx, tcnt, q, k, sel_k, blocksz=128, scratch=tk_scratch), 5, 2)
+    # the reference's own sparse operator (128-row query blocks, key-token lists, renormalising) on those lists
+    ms_tok = ev_time(lambda: capi.sp_attn(o, q, k, v, kidx, tcnt), 5, 2)
+    F_tok = 4.0 * B * H * S * sel_k * D
     del kidx, tk_scratch
 
     step = lambda: torch.ops.cuda_attn.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
@@ -367,6 +370,7 @@ def main():
                 "packedmask_to_indexmask_frac_of_hbm_peak": pack_bytes / ms_p2i / 1e6 / peaks["hbm_gbs"],
                 "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
                 "topk_indices_ms": ms_topk, "topk_select_k": sel_k,
+                "sp_attn_tokens_ms": ms_tok, "sp_attn_tokens_tflops_on_listed_tokens": F_tok / ms_tok / 1e9,
                 "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
                 "sparse_ms": ms_step, "sparse_speedup_over_full": ms_full / ms_step,
                 "ideal_speedup_1_over_density": 1.0 / density,
