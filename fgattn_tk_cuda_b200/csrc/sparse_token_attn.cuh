@@ -1,6 +1,6 @@
 // Sparse attention over key-TOKEN lists at the reference granularity (128-row query blocks).
 // For each query block the listed K/V rows are gathered 128 at a time into swizzled shared-memory
-// tiles (16-byte cp.async per chunk, whole rows per warp-wide copy, seven gather warps), and the flash-attention step over the
+// tiles (16-byte cp.async per chunk, whole rows per warp-wide copy, fifteen gather warps), and the flash-attention step over the
 // gathered keys runs on tcgen05 with an online (renormalising) softmax.  A CTA runs two query
 // blocks ("slots") against one tensor pipe; their K/V tiles share one ring in consumption order.
 // List entries >= the number of key rows, and slots past the count, are masked out.
@@ -26,7 +26,7 @@ struct TokenCfg {
   static constexpr int kHalves = D / 64;
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kStages = (D == 128) ? 4 : 8;
-  static constexpr int kGatherWarps = 7;                  // the copies a warp can keep in flight are the limit
+  static constexpr int kGatherWarps = 15;                 // the copies a warp can keep in flight are the limit
   static constexpr int kGatherThreads = 32 * kGatherWarps;
   static constexpr int kThreads = 32 * (8 + 1 + kGatherWarps);   // 8 softmax warps, the UMMA issuer, the gather warps
   static constexpr int kOffQ = 0;
@@ -43,6 +43,82 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+
+// Online softmax over one 128-column score tile in two passes of 32-column quarters, so that a thread
+// never holds more than 32 scores: pass 1 finds the row maximum over the live columns (colmask: 4
+// words, bit set = live), pass 2 re-reads the scores, writes the bf16 probabilities over the first 64
+// columns of the same tile and adds up the row sum.  The accumulator row is rescaled lazily (2^8 rule).
+template <int D>
+__device__ __forceinline__ void softmax_online_quarters(uint32_t s_addr, uint32_t o_addr, float c, bool first,
+                                                        OnlineState& st, const uint32_t (&colmask)[4]) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t mw = colmask[w];
+    if (mw == 0u) continue;                              // warp-uniform: no live column in this quarter
+    uint32_t r[32];
+    tmem_ld32(s_addr + w * 32, r);
+    tmem_ld_wait();
+    float c0 = -INFINITY, c1 = -INFINITY, c2 = -INFINITY, c3 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      c0 = fmaxf(c0, ((mw >> i) & 1u) ? __uint_as_float(r[i]) : -INFINITY);
+      c1 = fmaxf(c1, ((mw >> (i + 1)) & 1u) ? __uint_as_float(r[i + 1]) : -INFINITY);
+      c2 = fmaxf(c2, ((mw >> (i + 2)) & 1u) ? __uint_as_float(r[i + 2]) : -INFINITY);
+      c3 = fmaxf(c3, ((mw >> (i + 3)) & 1u) ? __uint_as_float(r[i + 3]) : -INFINITY);
+    }
+    mx = fmaxf(mx, fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)));
+  }
+  st.m_true = fmaxf(st.m_true, mx);
+  const float ms = mx * c;
+  const bool grow = ms > st.m_used + 8.0f;
+  if (__any_sync(0xffffffffu, grow)) {
+    const float alpha = grow ? ex2(st.m_used - ms) : 1.0f;
+    if (grow) st.m_used = ms;
+    st.l *= alpha;
+    if (!first) {
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + cc * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st32(o_addr + cc * 32, o);
+      }
+    }
+  }
+  const float neg_m = -st.m_used;
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t mw = colmask[w];
+    uint32_t pk[16];
+    if (mw != 0u) {
+      uint32_t r[32];
+      tmem_ld32(s_addr + w * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
+        float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+        if (!((mw >> i) & 1u)) p0 = 0.f;
+        if (!((mw >> (i + 1)) & 1u)) p1 = 0.f;
+        sum0 += p0;
+        sum1 += p1;
+        pk[i >> 1] = pack_bf16(p0, p1);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = 0u;
+    }
+    // quarter w's probabilities land on columns 16w .. 16w+15, all of them already consumed
+    tmem_st16(s_addr + w * 16, pk);
+  }
+  st.l += sum0 + sum1;
+  tmem_st_wait();
+}
 
 template <int D>
 __global__ void __launch_bounds__(TokenCfg<D>::kThreads, 1)
@@ -102,7 +178,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
 
   if (warp == 8 || warp >= 10) {
     // ------------------------------------------------------------------ gather producers
-    reg_dealloc<48>();
+    reg_dealloc<40>();
     if (warp == 8 && lane == 0) {
       tma_prefetch_desc(&mq);
       mbar_arrive_expect_tx(bar(TB_Q_FULL), 2 * Cfg::kTileBytes);
@@ -112,12 +188,12 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
                       bh);
     }
     __syncwarp();
-    const int gw = (warp == 8) ? 0 : warp - 9;                         // gather warp 0..6
+    const int gw = (warp == 8) ? 0 : warp - 9;                         // gather warp 0..14
     constexpr int kChunksPerRow = D / 8;                               // 16-byte chunks per row
     constexpr int kRowsPerInstr = 32 / kChunksPerRow;                  // rows one warp-wide copy covers
-    // rows of a 128-token tile are dealt to the seven gather warps in contiguous runs of 4 x 20 + 3 x 16;
+    // rows of a 128-token tile are dealt to the fifteen gather warps in contiguous runs of 2 x 12 + 13 x 8;
     // a lane keeps the token id of run row `lane` (and of `lane + 32` for runs longer than a warp)
-    const int row0 = (gw < 4) ? gw * 20 : 80 + (gw - 4) * 16, nrows = (gw < 4) ? 20 : 16;
+    const int row0 = (gw < 2) ? gw * 12 : 24 + (gw - 2) * 8, nrows = (gw < 2) ? 12 : 8;
     const int sub = lane / kChunksPerRow, ch = lane % kChunksPerRow;
     int idx = 0;
     bool ok = true;
@@ -178,7 +254,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
     if (!ok && warp == 8 && lane == 0) mbar_wait_brief(bar(TB_Q_FULL), 0);
   } else if (warp == 9) {
     // ------------------------------------------------------------------ UMMA issuer
-    reg_dealloc<48>();
+    reg_dealloc<40>();
     {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
@@ -229,7 +305,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
     }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
-    reg_alloc<208>();
+    reg_alloc<152>();
     const int t = warp >> 2, wq = warp & 3;
     const int row = q0 + t * 128 + wq * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
@@ -254,8 +330,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       ok = mbar_wait(bar(TB_S_FULL + t), j & 1, ab, p.err, 901);
       if (!ok) break;
       tc_fence_after();
-      float mx0, mx1;
-      softmax_online_step<D, true>(s_addr, s_addr, o_addr, 64, 64, p.scale_log2, j == 0, st, mx0, mx1, live);
+      softmax_online_quarters<D>(s_addr, o_addr, p.scale_log2, j == 0, st, live);
       tc_fence_before();
       mbar_arrive(bar(TB_P_FULL + t));
       fetch_live(j + 1);
