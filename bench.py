@@ -361,6 +361,8 @@ def main():
                 "full_attn_frac_of_peak": F_full / ms_full / 1e9 / peak,
                 "block_lists_ms": ms_lists, "block_lists_qk_tflops": F_full / 2 / ms_lists / 1e9,
                 "maxq_denom_ms": ms_maxq, "maxq_denom_qk_tflops": F_full / 2 / ms_maxq / 1e9,
+                "mask_epilogue_note": "block_lists_ms - maxq_denom_ms (difference of two timings; the compaction "
+                                      "kernel alone is profiled in profiles/block_threshold_compact_c3_16heads.md)",
                 "mask_epilogue_ms": ms_lists - ms_maxq,
                 "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
                 "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
