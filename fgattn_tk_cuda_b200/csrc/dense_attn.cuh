@@ -29,6 +29,11 @@ struct DenseParams {
   int* err;             // device error word
   int S, S_pad, kv_len, n_kv_tiles, nkb, mask_stride;
   int bh0;              // first (batch*head) unit of this launch (blockmax is relative to it)
+  // kTokenMask, optional: key-block lists of the 64-row query blocks ([BH, nqb64, list_stride], counts
+  // [BH, nqb64]); a CTA then visits only the 128-key tiles that some list of its four query blocks names
+  const int* kb_idx;
+  const int* kb_cnt;
+  int list_stride, nqb64;
   float scale_log2;     // softmax scale * log2(e)
   float log2_tau;       // kTokenMask
 };
@@ -42,7 +47,9 @@ struct DenseCfg {
   static constexpr int kOffK = 2 * kTileBytes;
   static constexpr int kOffV = kOffK + kKStages * kTileBytes;
   static constexpr int kOffBar = kOffV + kVStages * kTileBytes;
-  static constexpr int kSmemBytes = kOffBar + 1024 /*barriers + scratch*/ + 1024 /*alignment slack*/;
+  static constexpr int kOffTiles = kOffBar + 1024;       // kTokenMask with lists: [0] count, then tile ids, then bitmap
+  static constexpr int kMaxListedTiles = 1024;           // 131072 keys
+  static constexpr int kSmemBytes = kOffTiles + 4 * (1 + kMaxListedTiles) + 4 * (kMaxListedTiles / 32) + 1024 /*alignment slack*/;
 };
 
 // barrier slots (8 bytes each) inside the barrier block
@@ -77,7 +84,6 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.y;                  // (batch*head) unit within this launch
   const int q0 = blockIdx.x * 256;            // first query row of this CTA
-  const int n_tiles = p.n_kv_tiles;
 
   if (tid == 0) {
     ab->flag = 0;
@@ -101,10 +107,55 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
+  // kTokenMask with key-block lists: the 128-key tiles this CTA has to visit, ascending
+  int* s_tiles = reinterpret_cast<int*>(smem + Cfg::kOffTiles);        // [0] = count, [1..] = tile ids
+  const bool listed = (MODE == kTokenMask) && p.kb_idx != nullptr;
+  if (listed) {
+    uint32_t* bm = reinterpret_cast<uint32_t*>(s_tiles + 1 + Cfg::kMaxListedTiles);
+    const int words = (p.n_kv_tiles + 31) / 32;
+    for (int w = tid; w < words; w += blockDim.x) bm[w] = 0u;
+    __syncthreads();
+    for (int i = 0; i < 4; ++i) {
+      const int qb = (q0 >> 6) + i;
+      if (qb >= p.nqb64) break;
+      const size_t rowi = size_t(p.bh0 + bh) * p.nqb64 + qb;
+      const int n = min(p.kb_cnt[rowi], p.list_stride);
+      const int* src = p.kb_idx + rowi * p.list_stride;
+      for (int e = tid; e < n; e += blockDim.x) {
+        const int tile = src[e] >> 1;
+        if (tile >= 0 && tile < p.n_kv_tiles) atomicOr(&bm[tile >> 5], 1u << (tile & 31));
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int base = 0;
+      for (int w0 = 0; w0 < words; w0 += 32) {
+        const int w = w0 + lane;
+        uint32_t u = (w < words) ? bm[w] : 0u;
+        const int cnt = __popc(u);
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int n = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += n;
+        }
+        int off = base + incl - cnt;
+        while (u) {
+          const int bit = __ffs(u) - 1;
+          u &= u - 1;
+          s_tiles[1 + off++] = w * 32 + bit;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) s_tiles[0] = base;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int n_tiles = listed ? s_tiles[0] : p.n_kv_tiles;
+  auto tile_of = [&](int j) -> int { return listed ? s_tiles[1 + j] : j; };
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -127,7 +178,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         mbar_arrive_expect_tx(bar(BAR_K_FULL + ks), Cfg::kTileBytes);
         for (int h = 0; h < Cfg::kHalves; ++h)
           tma_load_3d(sbase + Cfg::kOffK + ks * Cfg::kTileBytes + h * 16384, &mk, bar(BAR_K_FULL + ks), h * 64,
-                      j * 128, p.bh0 + bh);
+                      tile_of(j) * 128, p.bh0 + bh);
         if (HAS_V) {
           const int vs = j % Cfg::kVStages, vf = j / Cfg::kVStages;
           if (vf > 0) ok = mbar_wait(bar(BAR_V_EMPTY + vs), (vf - 1) & 1, ab, p.err, 102);
@@ -246,7 +297,8 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint32_t s_addr = lane_base + (HAS_V ? t * 128 : (t * 2 + b) * 128);
-      const int kv_left = p.kv_len - j * 128;          // valid keys in this tile
+      const int key0 = tile_of(j) * 128;               // first key of this tile
+      const int kv_left = p.kv_len - key0;             // valid keys in this tile
       const int valid0 = min(64, kv_left), valid1 = max(0, min(64, kv_left - 64));
       if (MODE == kTokenMask) {
         // per-token keep bit: any row of the 128-row block with s*c - t_row > log2(tau)
@@ -268,7 +320,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         // the caller-zeroed mask is only ever set: four warps (32 rows each) OR into it
         if (q0 + t * 128 < p.S) {
           const int qblk = (q0 + t * 128) >> 7;
-          int* mrow = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + qblk) * p.mask_stride + j * 128;
+          int* mrow = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + qblk) * p.mask_stride + key0;
 #pragma unroll
           for (int w = 0; w < 4; ++w)
             if ((bits[w] >> lane) & 1u) atomicOr(mrow + w * 32 + lane, 1);

@@ -85,6 +85,20 @@ void booleanmask_128(torch::Tensor booleanmask, torch::Tensor o_max_q, torch::Te
                                       stream_of(q)), "booleanmask_128");
 }
 
+void booleanmask_128_listed(torch::Tensor booleanmask, torch::Tensor o_max_q, torch::Tensor o_denom, torch::Tensor q,
+                            torch::Tensor k, double threshold, torch::Tensor kb_indices, torch::Tensor kb_counts) {
+  check_bf16_4d(q, "q"); check_bf16_4d(k, "k");
+  check_dtype(booleanmask, at::kInt, "booleanmask");
+  check_dtype(o_max_q, at::kFloat, "o_max_q"); check_dtype(o_denom, at::kFloat, "o_denom");
+  check_dtype(kb_indices, at::kInt, "kb_indices"); check_dtype(kb_counts, at::kInt, "kb_counts");
+  c10::cuda::CUDAGuard guard(q.device());
+  check_status(fgattn_booleanmask_128_listed(booleanmask.data_ptr<int>(), float(threshold), int(booleanmask.size(3)),
+                                             o_max_q.data_ptr<float>(), o_denom.data_ptr<float>(), q.data_ptr(),
+                                             k.data_ptr(), kb_indices.data_ptr<int>(), kb_counts.data_ptr<int>(),
+                                             int(kb_indices.size(3)), q.size(0), q.size(1), q.size(2), q.size(3),
+                                             k.size(2), k.size(2), 0.f, stream_of(q)), "booleanmask_128_listed");
+}
+
 void booleanmask_to_indexmask(torch::Tensor kv_indices, torch::Tensor kv_numindices, torch::Tensor booleanmask,
                               int64_t seq) {
   check_dtype(kv_indices, at::kInt, "kv_indices"); check_dtype(kv_numindices, at::kInt, "kv_numindices");
@@ -223,6 +237,8 @@ void meta_aim(torch::Tensor, torch::Tensor, int64_t, int64_t, int64_t, int64_t) 
 void meta6(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor) {}
 void meta_bm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, double) {}
 void meta_b2i(torch::Tensor, torch::Tensor, torch::Tensor, int64_t) {}
+void meta_bml(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, double, torch::Tensor,
+              torch::Tensor) {}
 void meta8(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
            torch::Tensor) {}
 void meta_bil(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, c10::optional<torch::Tensor>, torch::Tensor,
@@ -244,6 +260,7 @@ TORCH_LIBRARY_FRAGMENT(cuda_attn, m) {
   m.def("booleanmask_128(Tensor (booleanmask!) booleanmask, Tensor o_max_q, Tensor o_denom, Tensor q, Tensor k, float threshold) -> ()");
   m.def("booleanmask_to_indexmask(Tensor (kv_indices!) kv_indices, Tensor (kv_numindices!) kv_numindices, Tensor booleanmask, int seq) -> ()");
   // block-granular additions
+  m.def("booleanmask_128_listed(Tensor (booleanmask!) booleanmask, Tensor o_max_q, Tensor o_denom, Tensor q, Tensor k, float threshold, Tensor kb_indices, Tensor kb_counts) -> ()");
   m.def("block_index_lists(Tensor (kb_indices!) kb_indices, Tensor (kb_counts!) kb_counts, Tensor (o_max_q!) o_max_q, Tensor (o_denom!) o_denom, Tensor(o!)? o, Tensor q, Tensor k, Tensor? v, float threshold, Tensor (scratch!) scratch) -> ()");
   m.def("sp_attn_blocks_ml(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts, Tensor max_q, Tensor denom) -> ()");
   m.def("sp_attn_blocks(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts) -> ()");
@@ -264,6 +281,7 @@ TORCH_LIBRARY_IMPL(cuda_attn, Meta, m) {
   m.impl("maxq_denom", meta4);
   m.impl("booleanmask_128", meta_bm);
   m.impl("booleanmask_to_indexmask", meta_b2i);
+  m.impl("booleanmask_128_listed", meta_bml);
   m.impl("block_index_lists", meta_bil);
   m.impl("sp_attn_blocks_ml", meta8);
   m.impl("sp_attn_blocks", meta6);
@@ -282,6 +300,7 @@ TORCH_LIBRARY_IMPL(cuda_attn, CUDA, m) {
   m.impl("maxq_denom", maxq_denom);
   m.impl("booleanmask_128", booleanmask_128);
   m.impl("booleanmask_to_indexmask", booleanmask_to_indexmask);
+  m.impl("booleanmask_128_listed", booleanmask_128_listed);
   m.impl("block_index_lists", block_index_lists);
   m.impl("sp_attn_blocks_ml", sp_attn_blocks_ml);
   m.impl("sp_attn_blocks", sp_attn_blocks);
@@ -300,6 +319,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("booleanmask_128", &booleanmask_128, "booleanmask_128");
   m.def("booleanmask_to_indexmask", &booleanmask_to_indexmask, "booleanmask_to_indexmask");
   m.def("fullattn_maxq_denom", &fullattn_maxq_denom, "fullattn_maxq_denom");
+  m.def("booleanmask_128_listed", &booleanmask_128_listed, "token mask inside the kept 64x64 blocks");
   m.def("block_index_lists", &block_index_lists, "one-pass m/l + key-block lists");
   m.def("sp_attn_blocks_ml", &sp_attn_blocks_ml, "block-sparse attention, precomputed m/l");
   m.def("sp_attn_blocks", &sp_attn_blocks, "block-sparse attention, renormalising");

@@ -233,14 +233,23 @@ int fgattn_maxq_denom(float* max_q, float* denom, const void* q, const void* k, 
   return launch_dense<fg::kML, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, static_cast<cudaStream_t>(stream));
 }
 
-int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
-                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_rows,
-                           int kv_seq_len, float scale, void* stream) {
+namespace {
+int token_mask_launch(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
+                      const void* q, const void* k, const int* kb_indices, const int* kb_counts, int list_stride,
+                      int batch, int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* stream) {
   if (!booleanmask || !max_q || !denom || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
   if (mask_stride < kv_seq_len) return FGATTN_INVALID_ARGUMENT;
   DenseSetup s;
   int r = dense_setup(s, q, k, nullptr, batch, heads, seq, D, kv_rows, kv_seq_len, scale);
   if (r) return r;
+  if (kb_indices) {
+    if (!kb_counts || list_stride < 1) return FGATTN_INVALID_ARGUMENT;
+    if (s.p.n_kv_tiles > fg::DenseCfg<128>::kMaxListedTiles) return FGATTN_UNSUPPORTED;
+    s.p.kb_idx = kb_indices;
+    s.p.kb_cnt = kb_counts;
+    s.p.list_stride = list_stride;
+    s.p.nqb64 = (seq + 63) / 64;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t n = size_t(batch) * heads * ((seq + 127) / 128) * mask_stride;
   FG_CUDA(cudaMemsetAsync(booleanmask, 0, n * sizeof(int), st));
@@ -250,6 +259,23 @@ int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, c
   s.p.mask_stride = mask_stride;
   s.p.log2_tau = log2f(threshold);
   return launch_dense<fg::kTokenMask, false>(D, s.mq, s.mk, s.mv, s.p, batch * heads, st);
+}
+}  // namespace
+
+int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, const float* max_q, const float* denom,
+                           const void* q, const void* k, int batch, int heads, int seq, int D, int kv_rows,
+                           int kv_seq_len, float scale, void* stream) {
+  return token_mask_launch(booleanmask, threshold, mask_stride, max_q, denom, q, k, nullptr, nullptr, 0, batch, heads,
+                           seq, D, kv_rows, kv_seq_len, scale, stream);
+}
+
+int fgattn_booleanmask_128_listed(int* booleanmask, float threshold, int mask_stride, const float* max_q,
+                                  const float* denom, const void* q, const void* k, const int* kb_indices,
+                                  const int* kb_counts, int list_stride, int batch, int heads, int seq, int D,
+                                  int kv_rows, int kv_seq_len, float scale, void* stream) {
+  if (!kb_indices || !kb_counts) return FGATTN_INVALID_ARGUMENT;
+  return token_mask_launch(booleanmask, threshold, mask_stride, max_q, denom, q, k, kb_indices, kb_counts, list_stride,
+                           batch, heads, seq, D, kv_rows, kv_seq_len, scale, stream);
 }
 
 int fgattn_booleanmask_to_indexmask(int* kv_indices, int* kv_num_indices, const int* booleanmask, int batch, int heads,

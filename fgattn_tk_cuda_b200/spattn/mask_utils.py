@@ -172,10 +172,22 @@ def qk_bitmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz=128):
     return mask
 
 
+def qk_token_mask_cuda(q, k, thresh, v=None):
+    """Token mask int32 [B,H,ceil(S/128),pad128(S_kv)] of the reference granularity in two cheap passes:
+    the one-pass 64x64 block pipeline (max_q, denom, key-block lists, and the dense output when v is
+    given), then the threshold test of python/spattn/mask_utils.py:337-354 only inside the kept blocks --
+    a token can pass only there.  Returns (mask, max_q, denom[, out])."""
+    kb_idx, kb_cnt, max_q, denom, *out = qk_block_indexmask_cuda(q, k, thresh, v=v)
+    B, H, S, _ = q.shape
+    mask = torch.empty((B, H, (S + 127) // 128, _pad128(k.shape[2])), device=q.device, dtype=torch.int32)
+    spattn_interface.booleanmask_128_listed(mask, max_q, denom, q.contiguous(), k.contiguous(), thresh, kb_idx, kb_cnt)
+    return (mask, max_q, denom, *out)
+
+
 def qk_bitmask_cuda(q, k, thresh, blocksz=128):
     """bool token mask (python/spattn/mask_utils.py:248-269)."""
-    max_q, denom = _maxq_denom(q, k)
-    return qk_bitmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz) > 0
+    assert blocksz == 128
+    return qk_token_mask_cuda(q, k, thresh)[0] > 0
 
 
 def bitmask_to_indexmask_cuda(booleanmask, seq=None):
@@ -232,8 +244,7 @@ def qk_indexmask_cuda(q, k, thresh, blocksz=128):
     if blocksz == 64:
         return qk_block_indexmask_cuda(q, k, thresh)
     assert blocksz == 128
-    max_q, denom = _maxq_denom(q, k)
-    return qk_indexmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz)
+    return bitmask_to_indexmask_cuda(qk_token_mask_cuda(q, k, thresh)[0], k.shape[2])
 
 
 # ------------------------------------------------------------------------------------------------

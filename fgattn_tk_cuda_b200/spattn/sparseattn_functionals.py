@@ -79,10 +79,10 @@ def compute_cache_and_attn_cuda(query, key, value, *args, **kwargs):
     if blocksz == 64:
         idx, cnt, max_q, denom, out = mask_utils.qk_block_indexmask_cuda(query, key, thresh, v=value)
         return out, idx, cnt, max_q, denom
-    out = _out(query)
-    max_q, denom = _ml(query)
-    spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(), value.contiguous())
-    idx, cnt = mask_utils.qk_indexmask_from_maxq_denom_cuda(max_q, denom, query, key, thresh, blocksz=blocksz)
+    # reference granularity: dense output, max_q / denom and the 64x64 block lists in one pass, then the
+    # token mask only inside the kept blocks, then the compaction
+    mask, _, _, out = mask_utils.qk_token_mask_cuda(query, key, thresh, v=value)
+    idx, cnt = mask_utils.bitmask_to_indexmask_cuda(mask, key.shape[2])
     return out, idx, cnt
 
 
@@ -109,12 +109,7 @@ def bitmaskcached_attn_cuda(query, key, value, current_layer, ditrun, *args, **k
     (sparseattn_functionals.py:116-134); reference granularity only."""
     mask_cache = kwargs["mask_cache"]
     if mask_cache.run_fullattn(ditrun):
-        out = _out(query)
-        max_q, denom = _ml(query)
-        spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(),
-                                             value.contiguous())
-        mask = mask_utils.qk_bitmask_from_maxq_denom_cuda(max_q, denom, query, key, kwargs["thresh"],
-                                                          blocksz=kwargs["blocksz"])
-        mask_cache.update_cache(current_layer, mask, query.shape[2])
+        mask, _, _, out = mask_utils.qk_token_mask_cuda(query, key, kwargs["thresh"], v=value)
+        mask_cache.update_cache(current_layer, mask, key.shape[2])
         return out
     return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer)[:2])

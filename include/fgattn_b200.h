@@ -76,6 +76,16 @@ int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, c
                            const void* q, const void* k, int batch, int heads, int seq, int D, int kv_rows,
                            int kv_seq_len, float scale, void* stream);
 
+/* Same token mask, computed only inside the 64x64 blocks that fgattn_block_index_lists kept for the
+ * same q, k and threshold (kb_indices / kb_counts / list_stride as that call wrote them, max_q / denom
+ * from the same call).  A token can only pass the threshold inside a kept block, so the result is the
+ * mask of fgattn_booleanmask_128 (up to scores within rounding of the threshold) while the second
+ * Q K^T pass of include/mask_utils.cuh:131-243 shrinks to the key tiles that some kept block touches. */
+int fgattn_booleanmask_128_listed(int* booleanmask, float threshold, int mask_stride, const float* max_q,
+                                  const float* denom, const void* q, const void* k, const int* kb_indices,
+                                  const int* kb_counts, int list_stride, int batch, int heads, int seq, int D,
+                                  int kv_rows, int kv_seq_len, float scale, void* stream);
+
 /* Mask rows -> ascending index lists: for every (b,h,seqblock) row of booleanmask
  * ([B,H,seqblocks,mask_stride] int32, > 0 = keep) write the kept columns < seq in ascending order
  * to kv_indices, fill the remaining slots with mask_stride and write the count.
