@@ -238,6 +238,11 @@ def main():
     # one-bit-per-entry mask kernels on a token mask of the reference granularity (int32 [B,H,S/128,S_pad],
     # 8 % kept): pack = 4 B read + 1/8 B written per entry; packed -> lists = 1/8 B read + 4 B written
     tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
+    # threshold token mask (reference granularity): the full second Q K^T pass against the pass that only
+    # visits the kept 64x64 blocks
+    ms_tokmask = ev_time(lambda: capi.booleanmask_128(tmask, max_q, denom, q, k, w.tau), 3, 1)
+    ms_tokmask_listed = ev_time(lambda: capi.booleanmask_128_listed(tmask, max_q, denom, q, k, w.tau, idx, cnt), 5, 2)
+    tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
     tpacked = torch.empty(B, H, tmask.shape[2], s_pad // 8, dtype=torch.uint8, device=dev)
     tidx = torch.empty_like(tmask)
     tcnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
@@ -366,6 +371,7 @@ def main():
                 "mask_epilogue_ms": ms_lists - ms_maxq,
                 "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
                 "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
+                "booleanmask_128_ms": ms_tokmask, "booleanmask_128_listed_ms": ms_tokmask_listed,
                 "pack_mask_ms": ms_pack, "pack_mask_gbs": pack_bytes / ms_pack / 1e6,
                 "pack_mask_frac_of_hbm_peak": pack_bytes / ms_pack / 1e6 / peaks["hbm_gbs"],
                 "packedmask_to_indexmask_ms": ms_p2i, "packedmask_to_indexmask_gbs": pack_bytes / ms_p2i / 1e6,
