@@ -6,7 +6,11 @@
 // (the input of the threshold epilogue that builds key-block lists), and
 //   kTokenMask : with m, l given, the 128-row x 1-token threshold mask (booleanmask_128).
 //
-// One CTA owns two 128-row query tiles that share every K/V tile.  Warp roles:
+// A work item is a pair of 128-row query tiles that share every K/V tile; CTAs are persistent and take
+// items blockIdx.x, blockIdx.x + gridDim.x, ... (item = unit * pairs + pair, so that the CTAs running at
+// one time share the K/V of a few heads in L2).  All barrier phases run on across items, so the TMA
+// producer fetches the next item's Q and first K/V tiles while the last steps of the current one are
+// still being computed, and tensor memory is allocated once per CTA.  Warp roles:
 //   warps 0-3  softmax of query tile 0 (one row per thread)      warp 8  TMA producer
 //   warps 4-7  softmax of query tile 1                            warp 9  UMMA issuer
 // S = Q K^T accumulates in tensor memory; the softmax warps read it with tcgen05.ld, write the
@@ -29,6 +33,7 @@ struct DenseParams {
   int* err;             // device error word
   int S, S_pad, kv_len, n_kv_tiles, nkb, mask_stride;
   int bh0;              // first (batch*head) unit of this launch (blockmax is relative to it)
+  int n_pairs, n_items; // query tile pairs per unit; work items of this launch (units * n_pairs)
   // kTokenMask, optional: key-block lists of the 64-row query blocks ([BH, nqb64, list_stride], counts
   // [BH, nqb64]); a CTA then visits only the 128-key tiles that some list of its four query blocks names
   const int* kb_idx;
@@ -63,10 +68,11 @@ enum : int {
   BAR_S_EMPTY = 21,  // +tile*2+buf
   BAR_P_FULL = 25,   // +tile
   BAR_O_FULL = 27,   // +tile
-  BAR_COUNT = 29
+  BAR_Q_EMPTY = 29,  // the item's last Q K^T product has been executed
+  BAR_COUNT = 30
 };
 
-template <int D, int MODE, bool BLOCKMAX>
+template <int D, int MODE, bool BLOCKMAX, bool PERSIST>
 __global__ void __launch_bounds__(384, 1)
 dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                   const __grid_constant__ CUtensorMap mv, const DenseParams p) {
@@ -82,12 +88,12 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * BAR_COUNT + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y;                  // (batch*head) unit within this launch
-  const int q0 = blockIdx.x * 256;            // first query row of this CTA
+  const int first_item = blockIdx.x, item_step = gridDim.x;
 
   if (tid == 0) {
     ab->flag = 0;
     mbar_init(bar(BAR_Q_FULL), 1);
+    mbar_init(bar(BAR_Q_EMPTY), 1);
     for (int s = 0; s < 4; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
       mbar_init(bar(BAR_K_EMPTY + s), 1);
@@ -109,8 +115,10 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   }
   // kTokenMask with key-block lists: the 128-key tiles this CTA has to visit, ascending
   int* s_tiles = reinterpret_cast<int*>(smem + Cfg::kOffTiles);        // [0] = count, [1..] = tile ids
+  // (such launches have one CTA per item)
   const bool listed = (MODE == kTokenMask) && p.kb_idx != nullptr;
   if (listed) {
+    const int bh = first_item / p.n_pairs, q0 = (first_item - bh * p.n_pairs) * 256;
     uint32_t* bm = reinterpret_cast<uint32_t*>(s_tiles + 1 + Cfg::kMaxListedTiles);
     const int words = (p.n_kv_tiles + 31) / 32;
     for (int w = tid; w < words; w += blockDim.x) bm[w] = 0u;
@@ -164,39 +172,48 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       tma_prefetch_desc(&mq);
       tma_prefetch_desc(&mk);
       if (HAS_V) tma_prefetch_desc(&mv);
-      mbar_arrive_expect_tx(bar(BAR_Q_FULL), 2 * Cfg::kTileBytes);
-      for (int t = 0; t < 2; ++t)
-        for (int h = 0; h < Cfg::kHalves; ++h)
-          tma_load_3d(sbase + Cfg::kOffQ + t * Cfg::kTileBytes + h * 16384, &mq, bar(BAR_Q_FULL), h * 64,
-                      q0 + t * 128, p.bh0 + bh);
       bool ok = true;
-      int j = 0;
-      for (; j < n_tiles && ok; ++j) {
-        const int ks = j % Cfg::kKStages, kf = j / Cfg::kKStages;
-        if (kf > 0) ok = mbar_wait(bar(BAR_K_EMPTY + ks), (kf - 1) & 1, ab, p.err, 101);
+      uint32_t g = 0;                       // K (and V) tiles requested so far by this CTA
+      int it = 0;                           // items whose Q has been requested
+      for (int item = first_item; item < p.n_items && ok; item += item_step) {
+        const int bh = item / p.n_pairs, q0 = (item - bh * p.n_pairs) * 256;
+        if (it > 0) ok = mbar_wait(bar(BAR_Q_EMPTY), (it - 1) & 1, ab, p.err, 100);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar(BAR_K_FULL + ks), Cfg::kTileBytes);
-        for (int h = 0; h < Cfg::kHalves; ++h)
-          tma_load_3d(sbase + Cfg::kOffK + ks * Cfg::kTileBytes + h * 16384, &mk, bar(BAR_K_FULL + ks), h * 64,
-                      tile_of(j) * 128, p.bh0 + bh);
-        if (HAS_V) {
-          const int vs = j % Cfg::kVStages, vf = j / Cfg::kVStages;
-          if (vf > 0) ok = mbar_wait(bar(BAR_V_EMPTY + vs), (vf - 1) & 1, ab, p.err, 102);
-          if (!ok) break;
-          mbar_arrive_expect_tx(bar(BAR_V_FULL + vs), Cfg::kTileBytes);
+        ++it;
+        mbar_arrive_expect_tx(bar(BAR_Q_FULL), 2 * Cfg::kTileBytes);
+        for (int t = 0; t < 2; ++t)
           for (int h = 0; h < Cfg::kHalves; ++h)
-            tma_load_3d(sbase + Cfg::kOffV + vs * Cfg::kTileBytes + h * 16384, &mv, bar(BAR_V_FULL + vs), h * 64,
-                        j * 128, p.bh0 + bh);
+            tma_load_3d(sbase + Cfg::kOffQ + t * Cfg::kTileBytes + h * 16384, &mq, bar(BAR_Q_FULL), h * 64,
+                        q0 + t * 128, p.bh0 + bh);
+        for (int j = 0; j < n_tiles && ok; ++j, ++g) {
+          const int ks = g % Cfg::kKStages, kf = g / Cfg::kKStages;
+          if (kf > 0) ok = mbar_wait(bar(BAR_K_EMPTY + ks), (kf - 1) & 1, ab, p.err, 101);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar(BAR_K_FULL + ks), Cfg::kTileBytes);
+          for (int h = 0; h < Cfg::kHalves; ++h)
+            tma_load_3d(sbase + Cfg::kOffK + ks * Cfg::kTileBytes + h * 16384, &mk, bar(BAR_K_FULL + ks), h * 64,
+                        tile_of(j) * 128, p.bh0 + bh);
+          if (HAS_V) {
+            const int vs = g % Cfg::kVStages, vf = g / Cfg::kVStages;
+            if (vf > 0) ok = mbar_wait(bar(BAR_V_EMPTY + vs), (vf - 1) & 1, ab, p.err, 102);
+            if (!ok) { ++g; break; }        // the K copy of this tile is in flight
+            mbar_arrive_expect_tx(bar(BAR_V_FULL + vs), Cfg::kTileBytes);
+            for (int h = 0; h < Cfg::kHalves; ++h)
+              tma_load_3d(sbase + Cfg::kOffV + vs * Cfg::kTileBytes + h * 16384, &mv, bar(BAR_V_FULL + vs), h * 64,
+                          j * 128, p.bh0 + bh);
+          }
         }
+        if (!PERSIST) break;
       }
       if (!ok) {
-        // let copies that are still in flight land before the CTA goes away
-        mbar_wait_brief(bar(BAR_Q_FULL), 0);
-        for (int s = 0; s < Cfg::kKStages; ++s) {
-          int last = -1;
-          for (int jj = s; jj < j + 1 && jj < n_tiles; jj += Cfg::kKStages) last = jj;
-          if (last >= 0) mbar_wait_brief(bar(BAR_K_FULL + s), (last / Cfg::kKStages) & 1);
-          if (HAS_V && last >= 0) mbar_wait_brief(bar(BAR_V_FULL + s), (last / Cfg::kVStages) & 1);
+        // let copies that are still in flight land before the CTA goes away: the last request to
+        // every stage (a V request exists for tile x iff its K request does, except possibly the last)
+        if (it > 0) mbar_wait_brief(bar(BAR_Q_FULL), (it - 1) & 1);
+        for (uint32_t s = 0; s < uint32_t(Cfg::kKStages); ++s) {
+          if (g <= s) continue;
+          const uint32_t last = ((g - 1 - s) / Cfg::kKStages) * Cfg::kKStages + s;   // last tile <= g-1 on stage s
+          mbar_wait_brief(bar(BAR_K_FULL + s), (last / Cfg::kKStages) & 1);
+          if (HAS_V) mbar_wait_brief(bar(BAR_V_FULL + s), (last / Cfg::kVStages) & 1);
         }
       }
     }
@@ -222,54 +239,71 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           umma_ts_elect(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
                   idesc_pv, (acc || ks > 0) ? 1u : 0u);
       };
-      bool ok = mbar_wait_warp(bar(BAR_Q_FULL), 0, ab, p.err, 201);
-      if (HAS_V) {
-        if (ok) ok = mbar_wait_warp(bar(BAR_K_FULL + 0), 0, ab, p.err, 202);
-        if (ok) {
-          tc_fence_after();
-          for (int t = 0; t < 2; ++t) {
-            issue_qk(t, 0, t * 128);
-            umma_commit_elect(bar(BAR_S_FULL + t * 2));
-          }
-          umma_commit_elect(bar(BAR_K_EMPTY + 0));
-        }
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const int vs = j % Cfg::kVStages;
-          ok = mbar_wait_warp(bar(BAR_V_FULL + vs), (j / Cfg::kVStages) & 1, ab, p.err, 203);
-          const bool more = (j + 1 < n_tiles);
-          const int ks = (j + 1) % Cfg::kKStages;
-          if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((j + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
-          for (int t = 0; t < 2 && ok; ++t) {
-            ok = mbar_wait_warp(bar(BAR_P_FULL + t), j & 1, ab, p.err, 205);
-            if (!ok) break;
+      bool ok = true;
+      uint32_t g0 = 0;                      // K/V tiles of the items before this one
+      int it = 0;
+      for (int item = first_item; item < p.n_items && ok; item += item_step, ++it, g0 += n_tiles) {
+        ok = mbar_wait_warp(bar(BAR_Q_FULL), it & 1, ab, p.err, 201);
+        if (HAS_V) {
+          // P(t) lives over S(t) and the tensor pipe runs in order, so the first product of an item may
+          // follow the last P V of the previous one at once; O(t) is overwritten by the P V of step 0,
+          // which waits for a P that the softmax warps write only after they have read the old O(t).
+          if (ok) ok = mbar_wait_warp(bar(BAR_K_FULL + g0 % Cfg::kKStages), (g0 / Cfg::kKStages) & 1, ab, p.err, 202);
+          if (ok) {
             tc_fence_after();
-            issue_pv(t, vs, j > 0);
-            if (more) {
-              issue_qk(t, ks, t * 128);
+            for (int t = 0; t < 2; ++t) {
+              issue_qk(t, g0 % Cfg::kKStages, t * 128);
               umma_commit_elect(bar(BAR_S_FULL + t * 2));
-            } else {
-              umma_commit_elect(bar(BAR_O_FULL + t));
+            }
+            umma_commit_elect(bar(BAR_K_EMPTY + g0 % Cfg::kKStages));
+            if (n_tiles == 1) umma_commit_elect(bar(BAR_Q_EMPTY));
+          }
+          for (int j = 0; j < n_tiles && ok; ++j) {
+            const uint32_t g = g0 + j;
+            const int vs = g % Cfg::kVStages;
+            ok = mbar_wait_warp(bar(BAR_V_FULL + vs), (g / Cfg::kVStages) & 1, ab, p.err, 203);
+            const bool more = (j + 1 < n_tiles);
+            const int ks = (g + 1) % Cfg::kKStages;
+            if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((g + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
+            for (int t = 0; t < 2 && ok; ++t) {
+              ok = mbar_wait_warp(bar(BAR_P_FULL + t), g & 1, ab, p.err, 205);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv(t, vs, j > 0);
+              if (more) {
+                issue_qk(t, ks, t * 128);
+                umma_commit_elect(bar(BAR_S_FULL + t * 2));
+              } else {
+                umma_commit_elect(bar(BAR_O_FULL + t));
+              }
+            }
+            if (ok) {
+              umma_commit_elect(bar(BAR_V_EMPTY + vs));
+              if (more) umma_commit_elect(bar(BAR_K_EMPTY + ks));
+              if (j + 2 == n_tiles) umma_commit_elect(bar(BAR_Q_EMPTY));
             }
           }
-          if (ok) {
-            umma_commit_elect(bar(BAR_V_EMPTY + vs));
-            if (more) umma_commit_elect(bar(BAR_K_EMPTY + ks));
+        } else {
+          // no V: S is double-buffered per query tile; tile t, buffer b lives at column (2t+b)*128
+          for (int j = 0; j < n_tiles && ok; ++j) {
+            const uint32_t g = g0 + j;
+            const int ks = g % Cfg::kKStages, b = g & 1;
+            const uint32_t f = g >> 1;
+            ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (g / Cfg::kKStages) & 1, ab, p.err, 206);
+            for (int t = 0; t < 2 && ok; ++t) {
+              if (f > 0) ok = mbar_wait_warp(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(t, ks, (t * 2 + b) * 128);
+              umma_commit_elect(bar(BAR_S_FULL + t * 2 + b));
+            }
+            if (ok) {
+              umma_commit_elect(bar(BAR_K_EMPTY + ks));
+              if (j + 1 == n_tiles) umma_commit_elect(bar(BAR_Q_EMPTY));
+            }
           }
         }
-      } else {
-        // no V: S is double-buffered per query tile; tile t, buffer b lives at column (2t+b)*128
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const int ks = j % Cfg::kKStages, b = j & 1, f = j >> 1;
-          ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (j / Cfg::kKStages) & 1, ab, p.err, 206);
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (f > 0) ok = mbar_wait_warp(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(t, ks, (t * 2 + b) * 128);
-            umma_commit_elect(bar(BAR_S_FULL + t * 2 + b));
-          }
-          if (ok) umma_commit_elect(bar(BAR_K_EMPTY + ks));
-        }
+        if (!PERSIST) break;
       }
     }
   } else if (warp < 8) {
@@ -278,85 +312,93 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     const int t = warp >> 2;                           // query tile of this warpgroup
     const int wq = warp & 3;                           // TMEM lane quarter
     const int row_in_tile = wq * 32 + lane;
-    const int row = q0 + t * 128 + row_in_tile;        // query row in the sequence
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
     const float c = p.scale_log2;
-    const size_t ml_off = size_t(p.bh0 + bh) * p.S_pad + row;
-
-    OnlineState st;
-    online_init(st);
-    float t_row = INFINITY;       // kTokenMask: m*c + log2(l)
-    if (MODE == kTokenMask) {
-      if (row < p.S) t_row = p.max_q[ml_off] * c + log2f(p.denom[ml_off]);
-    }
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int b = HAS_V ? 0 : (j & 1);
-      const int fpar = HAS_V ? (j & 1) : ((j >> 1) & 1);
-      ok = mbar_wait(bar(BAR_S_FULL + t * 2 + b), fpar, ab, p.err, 301);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t s_addr = lane_base + (HAS_V ? t * 128 : (t * 2 + b) * 128);
-      const int key0 = tile_of(j) * 128;               // first key of this tile
-      const int kv_left = p.kv_len - key0;             // valid keys in this tile
-      const int valid0 = min(64, kv_left), valid1 = max(0, min(64, kv_left - 64));
+    uint32_t g0 = 0;                                   // K/V tiles of the items before this one
+    int it = 0;
+    for (int item = first_item; item < p.n_items && ok; item += item_step, ++it, g0 += n_tiles) {
+      const int bh = item / p.n_pairs, q0 = (item - bh * p.n_pairs) * 256;
+      const int row = q0 + t * 128 + row_in_tile;      // query row in the sequence
+      const size_t ml_off = size_t(p.bh0 + bh) * p.S_pad + row;
+
+      OnlineState st;
+      online_init(st);
+      float t_row = INFINITY;       // kTokenMask: m*c + log2(l)
       if (MODE == kTokenMask) {
-        // per-token keep bit: any row of the 128-row block with s*c - t_row > log2(tau)
-        const float thr = p.log2_tau + t_row;
-        uint32_t bits[4];
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + w * 32, r);
-          tmem_ld_wait();
-          uint32_t m = 0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            m |= (__uint_as_float(r[i]) * c > thr && w * 32 + i < kv_left) ? (1u << i) : 0u;
-          bits[w] = __reduce_or_sync(0xffffffffu, m);
-        }
-        tc_fence_before();
-        mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
-        // the caller-zeroed mask is only ever set: four warps (32 rows each) OR into it
-        if (q0 + t * 128 < p.S) {
-          const int qblk = (q0 + t * 128) >> 7;
-          int* mrow = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + qblk) * p.mask_stride + key0;
-#pragma unroll
-          for (int w = 0; w < 4; ++w)
-            if ((bits[w] >> lane) & 1u) atomicOr(mrow + w * 32 + lane, 1);
-        }
-        continue;
+        if (row < p.S) t_row = p.max_q[ml_off] * c + log2f(p.denom[ml_off]);
       }
-      float mx0, mx1;
-      softmax_online_step<D, HAS_V>(s_addr, lane_base + t * 128, lane_base + 256 + t * 128, valid0, valid1, c, j == 0,
-                                    st, mx0, mx1);
-      tc_fence_before();
-      if (HAS_V) mbar_arrive(bar(BAR_P_FULL + t));
-      else mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
-      if (BLOCKMAX) {
-        if (row < p.S_pad) {
-          float* bm = p.blockmax + (size_t(bh) * p.nkb + size_t(j) * 2) * p.S_pad + row;
-          bm[0] = mx0;
-          if (j * 2 + 1 < p.nkb) bm[p.S_pad] = mx1;
-        }
-      }
-    }
-    // ---- epilogue
-    if (ok && WRITE_ML) {
-      if (row < p.S) {
-        p.max_q[ml_off] = st.m_true;
-        p.denom[ml_off] = st.l * ex2(st.m_used - st.m_true * c);
-      } else if (row < p.S_pad) {
-        p.max_q[ml_off] = 0.f;
-        p.denom[ml_off] = -INFINITY;
-      }
-    }
-    if (ok && HAS_V) {
-      ok = mbar_wait(bar(BAR_O_FULL + t), 0, ab, p.err, 302);
-      if (ok) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t g = g0 + j;
+        const int b = HAS_V ? 0 : int(g & 1);
+        const uint32_t fpar = HAS_V ? (g & 1) : ((g >> 1) & 1);
+        ok = mbar_wait(bar(BAR_S_FULL + t * 2 + b), fpar, ab, p.err, 301);
+        if (!ok) break;
         tc_fence_after();
-        store_o_row<D>(lane_base + 256 + t * 128, p.o + (size_t(p.bh0 + bh) * p.S + row) * D, 1.0f / st.l, row < p.S);
+        const uint32_t s_addr = lane_base + (HAS_V ? t * 128 : (t * 2 + b) * 128);
+        const int key0 = tile_of(j) * 128;               // first key of this tile
+        const int kv_left = p.kv_len - key0;             // valid keys in this tile
+        const int valid0 = min(64, kv_left), valid1 = max(0, min(64, kv_left - 64));
+        if (MODE == kTokenMask) {
+          // per-token keep bit: any row of the 128-row block with s*c - t_row > log2(tau)
+          const float thr = p.log2_tau + t_row;
+          uint32_t bits[4];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            uint32_t r[32];
+            tmem_ld32(s_addr + w * 32, r);
+            tmem_ld_wait();
+            uint32_t m = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              m |= (__uint_as_float(r[i]) * c > thr && w * 32 + i < kv_left) ? (1u << i) : 0u;
+            bits[w] = __reduce_or_sync(0xffffffffu, m);
+          }
+          tc_fence_before();
+          mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
+          // the caller-zeroed mask is only ever set: four warps (32 rows each) OR into it
+          if (q0 + t * 128 < p.S) {
+            const int qblk = (q0 + t * 128) >> 7;
+            int* mrow = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + qblk) * p.mask_stride + key0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+              if ((bits[w] >> lane) & 1u) atomicOr(mrow + w * 32 + lane, 1);
+          }
+          continue;
+        }
+        float mx0, mx1;
+        softmax_online_step<D, HAS_V>(s_addr, lane_base + t * 128, lane_base + 256 + t * 128, valid0, valid1, c, j == 0,
+                                      st, mx0, mx1);
+        tc_fence_before();
+        if (HAS_V) mbar_arrive(bar(BAR_P_FULL + t));
+        else mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
+        if (BLOCKMAX) {
+          if (row < p.S_pad) {
+            float* bm = p.blockmax + (size_t(bh) * p.nkb + size_t(j) * 2) * p.S_pad + row;
+            bm[0] = mx0;
+            if (j * 2 + 1 < p.nkb) bm[p.S_pad] = mx1;
+          }
+        }
       }
+      // ---- epilogue of the item
+      if (ok && WRITE_ML) {
+        if (row < p.S) {
+          p.max_q[ml_off] = st.m_true;
+          p.denom[ml_off] = st.l * ex2(st.m_used - st.m_true * c);
+        } else if (row < p.S_pad) {
+          p.max_q[ml_off] = 0.f;
+          p.denom[ml_off] = -INFINITY;
+        }
+      }
+      if (ok && HAS_V) {
+        ok = mbar_wait(bar(BAR_O_FULL + t), it & 1, ab, p.err, 302);
+        if (ok) {
+          tc_fence_after();
+          store_o_row<D>(lane_base + 256 + t * 128, p.o + (size_t(p.bh0 + bh) * p.S + row) * D, 1.0f / st.l, row < p.S);
+          tc_fence_before();       // the next item's first P V product overwrites O(t)
+        }
+      }
+      if (!PERSIST) break;
     }
   }
   else {

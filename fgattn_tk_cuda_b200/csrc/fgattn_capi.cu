@@ -71,17 +71,54 @@ int set_smem(K kernel, int bytes) {
   return FGATTN_OK;
 }
 
-// One launch of the dense family over heads [bh0, bh0 + nbh).
+// Streaming multiprocessors of the current device (looked up once per device).
+int sm_count(int* out) {
+  static int cached[64] = {0};
+  int dev = 0;
+  FG_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || cached[dev] == 0) {
+    int sms = 0;
+    FG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (dev < 0 || dev >= 64) { *out = sms; return FGATTN_OK; }
+    cached[dev] = sms;
+  }
+  *out = cached[dev];
+  return FGATTN_OK;
+}
+
+// One launch of the dense family over heads [bh0, bh0 + nbh).  Work item = pair of 128-row query tiles
+// of one unit.  PERSIST: one CTA per SM walks the items (pays off when an item has few key tiles, so
+// that the CTA prologue and the first loads would otherwise dominate); else one CTA per item.
+template <int D, int MODE, bool BLOCKMAX, bool PERSIST>
+int launch_dense_k(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const fg::DenseParams& p,
+                   int ctas, cudaStream_t st) {
+  auto kern = fg::dense_attn_kernel<D, MODE, BLOCKMAX, PERSIST>;
+  int r = set_smem(kern, fg::DenseCfg<D>::kSmemBytes);
+  if (r) return r;
+  kern<<<dim3(ctas, 1, 1), 384, fg::DenseCfg<D>::kSmemBytes, st>>>(mq, mk, mv, p);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
+constexpr int kPersistMaxKeyTiles = 8;     // persistent CTAs up to 1024 keys
+
 template <int D, int MODE, bool BLOCKMAX>
 int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const fg::DenseParams& p,
                    int nbh, cudaStream_t st) {
-  auto kern = fg::dense_attn_kernel<D, MODE, BLOCKMAX>;
-  int r = set_smem(kern, fg::DenseCfg<D>::kSmemBytes);
-  if (r) return r;
-  dim3 grid((p.S + 255) / 256, nbh, 1);
-  kern<<<grid, 384, fg::DenseCfg<D>::kSmemBytes, st>>>(mq, mk, mv, p);
-  FG_CUDA(cudaGetLastError());
-  return FGATTN_OK;
+  fg::DenseParams pp = p;
+  pp.n_pairs = (p.S + 255) / 256;
+  pp.n_items = pp.n_pairs * nbh;
+  if constexpr (MODE != fg::kTokenMask && !BLOCKMAX) {
+    static const int persist_env = getenv("FGATTN_DENSE_PERSIST") ? atoi(getenv("FGATTN_DENSE_PERSIST")) : -1;
+    const bool persist = persist_env >= 0 ? persist_env != 0 : p.n_kv_tiles <= kPersistMaxKeyTiles;
+    if (persist) {
+      int sms = 0;
+      int r = sm_count(&sms);
+      if (r) return r;
+      return launch_dense_k<D, MODE, BLOCKMAX, true>(mq, mk, mv, pp, pp.n_items < sms ? pp.n_items : sms, st);
+    }
+  }
+  return launch_dense_k<D, MODE, BLOCKMAX, false>(mq, mk, mv, pp, pp.n_items, st);
 }
 
 template <int MODE, bool BLOCKMAX>

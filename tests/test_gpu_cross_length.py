@@ -61,6 +61,35 @@ def test_dense_family(B, H, S, Skv, D, kv):
         assert ((ll[..., :S].cpu() - rl[..., :S]).abs() / rl[..., :S]).max() <= 2e-3
 
 
+@pytest.mark.parametrize("B,H,S,Skv,D,kv", [(1, 4, 15000, 300, 64, None), (2, 3, 13000, 1024, 128, 1000),
+                                             (1, 5, 9999, 128, 128, None)])
+def test_few_keys_many_query_tiles(B, H, S, Skv, D, kv):
+    """Up to 1024 keys the dense family runs persistent CTAs that walk several (unit, query tile pair)
+    items each; these shapes have more items than the GPU has SMs."""
+    from oracle import fgattn_oracle as orc
+    capi = _capi()
+    assert B * H * ((S + 255) // 256) > torch.cuda.get_device_properties(0).multi_processor_count
+    q, k, v = _inputs(B, H, S, Skv, D, S + 3 * Skv)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    s_pad = 128 * ((S + 127) // 128)
+    o = torch.full_like(qc, float("nan"))
+    capi.full_attn(o, qc, kc, vc, kv_seq_len=kv)
+    o2 = torch.full_like(qc, float("nan"))
+    m = torch.full((B, H, 1, s_pad), float("nan"), device="cuda")
+    l = torch.full_like(m, float("nan"))
+    capi.fullattn_maxq_denom(o2, m, l, qc, kc, vc, kv_seq_len=kv)
+    m2, l2 = torch.full_like(m, float("nan")), torch.full_like(m, float("nan"))
+    capi.maxq_denom(m2, l2, qc, kc, kv_seq_len=kv)
+    capi.check()
+    _close(o, orc.full_attn(q, k, v, kv_seq_len=kv))
+    assert torch.equal(o, o2)
+    rm, rl = orc.maxq_denom(q, k, kv_seq_len=kv)
+    for mm, ll in ((m, l), (m2, l2)):
+        assert (mm[..., :S].cpu() - rm[..., :S]).abs().max() <= 2e-3
+        assert ((ll[..., :S].cpu() - rl[..., :S]).abs() / rl[..., :S]).max() <= 2e-3
+        assert (mm[..., S:] == 0).all() and torch.isinf(ll[..., S:]).all()
+
+
 @pytest.mark.parametrize("B,H,S,Skv,D,kv", SHAPES)
 def test_block_pipeline(B, H, S, Skv, D, kv):
     from oracle import fgattn_oracle as orc
