@@ -145,6 +145,7 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, nargs="*", default=None, help="stages: sequence lengths (default 32760 75600)")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--model-heads", type=int, default=MODEL_HEADS, help="model: heads (default 40)")
     ap.add_argument("--sdpa", action="store_true", help="model: also time torch's scaled_dot_product_attention")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
@@ -154,7 +155,7 @@ def main(argv=None):
             for s in (a.seq or STAGE_SEQS):
                 stage_table(h, s, a.reps, a.warmup)
     if a.table in ("model", "all"):
-        model_table(a.reps, a.warmup, sdpa=a.sdpa)
+        model_table(a.reps, a.warmup, heads=a.model_heads, sdpa=a.sdpa)
 
 
 if __name__ == "__main__":
