@@ -261,6 +261,8 @@ def main():
     ms_tok = ev_time(lambda: capi.sp_attn(o, q, k, v, kidx, tcnt), 5, 2)
     F_tok = 4.0 * B * H * S * sel_k * D
     del kidx, tk_scratch
+    # replay of a cached mask: the renormalising block kernel on the same key-block lists
+    ms_renorm = ev_time(lambda: torch.ops.cuda_attn.sp_attn_blocks(o, q, k, v, idx, cnt), 10, 3)
 
     step = lambda: torch.ops.cuda_attn.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
 
@@ -379,6 +381,8 @@ def main():
                 "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
                 "topk_indices_ms": ms_topk, "topk_select_k": sel_k,
                 "sp_attn_tokens_ms": ms_tok, "sp_attn_tokens_tflops_on_listed_tokens": F_tok / ms_tok / 1e9,
+                "sp_attn_blocks_renorm_ms": ms_renorm,
+                "sp_attn_blocks_renorm_tflops_on_kept_blocks": F_sparse / ms_renorm / 1e9,
                 "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
                 "sparse_ms": ms_step, "sparse_speedup_over_full": ms_full / ms_step,
                 "ideal_speedup_1_over_density": 1.0 / density,

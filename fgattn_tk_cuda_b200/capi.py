@@ -43,7 +43,7 @@ PROTOTYPES = {
     "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
-    "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "fgattn_topk_scratch_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "fgattn_topk_indices": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "fgattn_pack_mask": (_i, [_vp, _vp, _i, _ll, _i, _vp]),
@@ -221,12 +221,19 @@ def sp_attn_blocks_ml(o, q, k, v, kb_indices, kb_counts, max_q, denom, kv_seq_le
               workspace.numel() * workspace.element_size(), _stream(q))
 
 
-def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0):
+def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0, workspace=None, ordered=True):
+    """ordered: thread blocks take the longest lists first (needs the workspace, allocated here when not
+    given); ordered=False runs them in storage order with no workspace."""
     _check_qkv(o, q, k, v)
     B, H, S, D = q.shape
+    if ordered and workspace is None:
+        workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
+    ws_ptr = _ptr(workspace) if ordered else None
+    ws_bytes = workspace.numel() * workspace.element_size() if ordered else 0
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn_blocks", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
-              kb_indices.shape[3], B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale, _stream(q))
+              kb_indices.shape[3], B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale, ws_ptr, ws_bytes,
+              _stream(q))
 
 
 # ---- one-bit-per-entry masks ----------------------------------------------------------------------

@@ -153,11 +153,14 @@ int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int 
 
 // Renormalising block-sparse attention (two-slot kernel).
 int launch_sparse(void* o, const void* q, const void* k, const void* v, const int* kb_idx, const int* kb_cnt,
-                  int list_stride, int B, int H, int S, int D, int kv_rows, int kv_len, float scale, cudaStream_t st) {
+                  int list_stride, int B, int H, int S, int D, int kv_rows, int kv_len, float scale, void* workspace,
+                  size_t workspace_bytes, cudaStream_t st) {
   int r = check_qk(q, k, B, H, S, D, kv_rows, kv_len);
   if (r) return r;
   if (!o || !v || !kb_idx || !kb_cnt) return FGATTN_INVALID_ARGUMENT;
   if (!aligned16(o) || !aligned16(v)) return FGATTN_MISALIGNED;
+  if (workspace && !aligned16(workspace)) return FGATTN_MISALIGNED;
+  if (workspace && workspace_bytes < fgattn_sp_attn_workspace_bytes(B, H, S)) return FGATTN_SCRATCH_TOO_SMALL;
   fg::SparseParams p;
   memset(&p, 0, sizeof(p));
   p.o = static_cast<__nv_bfloat16*>(o);
@@ -178,7 +181,23 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
   if (fg::make_qkv_map(&mq, q, B * H, S, D, 128) || fg::make_qkv_map(&mk, k, B * H, kv_rows, D, 64) ||
       fg::make_qkv_map(&mv, v, B * H, kv_rows, D, 64))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
-  dim3 grid((S + 255) / 256, B * H, 1);
+  p.quads = (S + 255) / 256;
+  const int n_units = B * H;
+  if ((long long)n_units * p.quads > 2147483647LL) return FGATTN_UNSUPPORTED;
+  if (workspace) {
+    // CTA order: units in groups whose K/V (<= 64 MiB) stays in L2, inside a group longest lists first
+    const size_t kv_bytes_per_unit = size_t(4) * kv_rows * D;
+    int group = int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit));
+    group = std::max(1, std::min(group, n_units));
+    const int n_groups = (n_units + group - 1) / group;
+    group = (n_units + n_groups - 1) / n_groups;                      // groups of equal size
+    int* ws = static_cast<int*>(workspace);
+    fg::sparse_order_kernel<<<(n_units + group - 1) / group, 256, 0, st>>>(kb_cnt, ws + 4, ws, p.nqb, p.quads, n_units,
+                                                                          group, 2);
+    FG_CUDA(cudaGetLastError());
+    p.order = ws + 4;
+  }
+  dim3 grid(n_units * p.quads, 1, 1);
   if (D == 128) {
     const int smem = fg::SparseCfg<128>::smem_bytes(p.list_cap, p.nkb);
     if (smem > 232448) return FGATTN_UNSUPPORTED;
@@ -651,9 +670,9 @@ int fgattn_indexmask_to_packedmask(unsigned char* packed, const int* indices, co
 
 int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                           const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_rows,
-                          int kv_seq_len, float scale, void* stream) {
+                          int kv_seq_len, float scale, void* workspace, size_t workspace_bytes, void* stream) {
   return launch_sparse(o, q, k, v, kb_indices, kb_counts, list_stride, batch, heads, seq, D, kv_rows, kv_seq_len, scale,
-                       static_cast<cudaStream_t>(stream));
+                       workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 // ---- top-k selector ------------------------------------------------------------------------------

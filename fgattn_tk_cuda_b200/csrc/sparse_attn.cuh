@@ -23,6 +23,10 @@ struct SparseParams {
   const int* kb_cnt;         // [BH, nqb]
   int* err;
   int S, S_pad, kv_len, nqb, nkb, list_stride, list_cap;   // list_cap: union entries a slot can hold
+  // CTA i works on item order[i] (or i when order is null); item = unit * quads + quad, a quad being four
+  // 64-row query blocks.  An order with the long lists first keeps the end of the launch short.
+  const int* order;
+  int quads;
   float scale_log2;
 };
 
@@ -71,8 +75,9 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
   uint32_t* bitmaps = lists + 2 * p.list_cap;                                                          // [2][2][words]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int q0 = blockIdx.x * 256;
+  const int item = p.order ? p.order[blockIdx.x] : int(blockIdx.x);
+  const int bh = item / p.quads;
+  const int q0 = (item - bh * p.quads) * 256;
   const int words = (p.nkb + 31) / 32;
 
   if (tid == 0) {

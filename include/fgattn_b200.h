@@ -165,16 +165,19 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
                              int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream);
 
-/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs (work-queue counter + per-head processing
- * order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
+/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs and fgattn_sp_attn_blocks can use (work-queue
+ * counter + processing order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
  * two calls that may overlap on the device must not share it. */
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);
 
-/* Same gather kernel with the renormalising softmax of the sp_attn operator (softmax over the kept
- * keys only, include/sparseattn_asyncgatherload_padded.cuh:198-249) on key-block lists. */
+/* Block-sparse attention with the renormalising softmax of the sp_attn operator (softmax over the kept
+ * keys only, include/sparseattn_asyncgatherload_padded.cuh:198-249) on key-block lists.  `workspace`
+ * (fgattn_sp_attn_workspace_bytes, scratch) is optional: with it the thread blocks take the groups of
+ * query blocks longest list first, which shortens the end of the launch when list lengths differ; with
+ * a null workspace they run in storage order.  The result is the same either way. */
 int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                           const int* kb_counts, int list_stride, int batch, int heads, int seq, int D, int kv_rows,
-                          int kv_seq_len, float scale, void* stream);
+                          int kv_seq_len, float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- one-bit-per-entry masks (mask caches) ---------------------------------------------------
  * Entry e of a row lives in byte e / 8, bit e % 8 (least significant bit first): the format of pack /

@@ -51,6 +51,8 @@ def test_argument_validation_needs_no_device():
     assert lib.fgattn_maxq_denom(null, null, buf, buf, 1, 1, 64, 64, 64, 64, 0.0, null) == 1
     assert lib.fgattn_booleanmask_to_indexmask(buf, buf, buf, 1, 1, 64, 0, 128, null) == 1
     assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 64, 0.0, buf, 64, null) == 1
+    assert lib.fgattn_sp_attn_blocks(buf, buf, buf, buf, null, buf, 4, 1, 1, 64, 64, 64, 64, 0.0, null, 0, null) == 1
+    assert lib.fgattn_sp_attn_blocks(buf, buf, buf, buf, buf, buf, 4, 1, 1, 64, 64, 64, 64, 0.0, buf, 8, null) == 7
     # one-bit-per-entry masks
     assert lib.fgattn_pack_mask(null, buf, 4, 8, 64, null) == 1                             # null output
     assert lib.fgattn_pack_mask(buf, buf, 2, 8, 64, null) == 2                              # element size

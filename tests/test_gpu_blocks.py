@@ -149,6 +149,11 @@ def test_random_lists_both_modes(S, D, kv):
     capi.sp_attn_blocks(o_rn, qc, kc, vc, idxc, cntc, kv_seq_len=kv)
     capi.check()
     _close(o_rn, orc.sp_attn_blocks(q, k, v, idx, cnt, kv_seq_len=kv))
+    # the order in which the thread blocks take the query blocks changes nothing in the result
+    o_st = torch.full_like(qc, float("nan"))
+    capi.sp_attn_blocks(o_st, qc, kc, vc, idxc, cntc, kv_seq_len=kv, ordered=False)
+    capi.check()
+    assert torch.equal(o_st, o_rn)
 
 
 def test_identity_lists_equal_dense():
