@@ -34,7 +34,7 @@ PROTOTYPES = {
                                            _vp]),
     "fgattn_booleanmask_to_indexmask": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "fgattn_all_index_mask": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "fgattn_sp_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
+    "fgattn_sp_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "fgattn_block_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _f, _vp,
                                       _sz, _vp]),
@@ -168,12 +168,18 @@ def all_index_mask(kv_indices, kv_num_indices, batch, heads, seqblocks, seq):
               kv_indices.shape[3], _stream(kv_indices))
 
 
-def sp_attn(o, q, k, v, kv_indices, kv_num_indices, scale=0.0):
+def sp_attn(o, q, k, v, kv_indices, kv_num_indices, scale=0.0, workspace=None, ordered=True):
+    """ordered: thread blocks take the longest lists first (needs the workspace, allocated here when not
+    given); ordered=False runs them in storage order with no workspace."""
     _check_qkv(o, q, k, v)
     B, H, S, D = q.shape
+    if ordered and workspace is None:
+        workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
+    ws_ptr = _ptr(workspace) if ordered else None
+    ws_bytes = workspace.numel() * workspace.element_size() if ordered else 0
     with torch.cuda.device(q.device):
         _call("fgattn_sp_attn", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kv_indices), _ptr(kv_num_indices),
-              kv_indices.shape[3], B, H, S, D, k.shape[2], scale, _stream(q))
+              kv_indices.shape[3], B, H, S, D, k.shape[2], scale, ws_ptr, ws_bytes, _stream(q))
 
 
 def block_scratch_bytes(B, H, S, kv_seq_len=None) -> int:

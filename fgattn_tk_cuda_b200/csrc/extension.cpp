@@ -49,9 +49,13 @@ void sp_attn(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Tensor v,
   check_bf16_4d(o, "o"); check_bf16_4d(q, "q"); check_bf16_4d(k, "k"); check_bf16_4d(v, "v");
   check_dtype(kv_indices, at::kInt, "kv_indices"); check_dtype(kv_num_indices, at::kInt, "kv_num_indices");
   c10::cuda::CUDAGuard guard(q.device());
+  // scratch for the longest-first order of the thread blocks, from the stream-ordered caching allocator
+  const int64_t ws_bytes = int64_t(fgattn_sp_attn_workspace_bytes(q.size(0), q.size(1), q.size(2)));
+  torch::Tensor ws = torch::empty({ws_bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
   check_status(fgattn_sp_attn(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), kv_indices.data_ptr<int>(),
                               kv_num_indices.data_ptr<int>(), int(kv_indices.size(3)), q.size(0), q.size(1),
-                              q.size(2), q.size(3), k.size(2), 0.f, stream_of(q)), "sp_attn");
+                              q.size(2), q.size(3), k.size(2), 0.f, ws.data_ptr(), size_t(ws_bytes), stream_of(q)),
+               "sp_attn");
 }
 
 void fullattn_maxq_denom(torch::Tensor o, torch::Tensor o_max_q, torch::Tensor o_denom, torch::Tensor q,

@@ -584,13 +584,16 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 
 // Queue order.  Heads are taken in groups of `group_heads` consecutive (batch, head) units (few
 // enough that the K/V of one group stays in L2, many enough that a group has several items per SM);
-// inside a group all query-block pairs are ordered longest list first, so that the long items start
-// early and the tail of the launch is made of short ones.  order[] receives global item ids
-// (unit * npairs + pair; with pairs_per_item = 2 an item is two pairs and npairs counts those items).
-// Counting sort on the list length; ties land in arbitrary order, which only affects scheduling.  grid (number of groups), 256 threads.  Block 0 also clears the queue counter.
+// inside a group all items are ordered longest first, so that the long items start early and the
+// tail of the launch is made of short ones.  order[] receives global item ids (unit * n_items + item).
+// An item is `subs` sub-items that are walked side by side (the longest counts), a sub-item is the
+// union of `elems` consecutive lists (their lengths are added): the persistent block kernel has
+// subs 1 / elems 2, the two-slot block kernel 2 / 2, the token-list kernel 2 / 1.  Lengths are
+// bucketed as (length >> shift).  Counting sort; ties land in arbitrary order, which only affects
+// scheduling.  grid (number of groups), 256 threads.  Block 0 also clears the queue counter.
 __global__ void __launch_bounds__(256)
 sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int* __restrict__ queue, int nqb,
-                    int npairs, int n_units, int group_heads, int pairs_per_item = 1) {
+                    int npairs, int n_units, int group_heads, int subs = 1, int elems = 2, int shift = 0) {
   constexpr int kBuckets = 1024;
   __shared__ int hist[kBuckets];
   __shared__ int part[256];
@@ -600,17 +603,18 @@ sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int
   if (blockIdx.x == 0 && tid == 0) *queue = 0;
   for (int i = tid; i < kBuckets; i += 256) hist[i] = 0;
   __syncthreads();
-  // items of pairs_per_item query-block pairs that are walked side by side: the longest pair counts
   auto length_of = [&](int i) {
     const int unit = u0 + i / npairs, it = i % npairs;
     int len = 0;
-    for (int j = 0; j < pairs_per_item; ++j) {
-      const int qb = 2 * (it * pairs_per_item + j);
-      const int a = (qb < nqb) ? kb_cnt[size_t(unit) * nqb + qb] : 0;
-      const int b = (qb + 1 < nqb) ? kb_cnt[size_t(unit) * nqb + qb + 1] : 0;
-      len = max(len, a + b);
+    for (int j = 0; j < subs; ++j) {
+      int sum = 0;
+      for (int e = 0; e < elems; ++e) {
+        const int qb = (it * subs + j) * elems + e;
+        if (qb < nqb) sum += max(kb_cnt[size_t(unit) * nqb + qb], 0);
+      }
+      len = max(len, sum);
     }
-    return min(max(len, 0), kBuckets - 1);
+    return min(len >> shift, kBuckets - 1);
   };
   for (int i = tid; i < n; i += 256) atomicAdd(&hist[length_of(i)], 1);
   __syncthreads();

@@ -18,6 +18,10 @@ struct TokenParams {
   const int* kv_cnt;        // [BH, nqb128]
   int* err;
   int S, S_kv, nqb, mask_stride;   // query rows, rows of k / v per head
+  // thread block i works on item order[i] (or i when order is null); item = unit * pairs + pair of
+  // 128-row query blocks
+  const int* order;
+  int pairs;
   float scale_log2;
 };
 
@@ -133,8 +137,9 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
   AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * TB_COUNT + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y;
-  const int q0 = blockIdx.x * 256;
+  const int item = p.order ? p.order[blockIdx.x] : int(blockIdx.x);
+  const int bh = item / p.pairs;
+  const int q0 = (item - bh * p.pairs) * 256;
 
   if (tid == 0) {
     ab->flag = 0;

@@ -103,10 +103,12 @@ int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int h
  * block, softmax restricted to the listed key tokens (renormalised), times the listed v rows.
  * kv_indices int32 [B,H,ceil(S/128),mask_stride], kv_num_indices int32 [B,H,ceil(S/128)].
  * Replaces attn_sparse_fwd_wg_impl (python/extension.cpp:10-14, python/cuda_attn.cu:41-75), the
- * sp_attn operator (python/extension.cpp:125-154). */
+ * sp_attn operator (python/extension.cpp:125-154).  `workspace` (fgattn_sp_attn_workspace_bytes, scratch)
+ * is optional: with it the thread blocks take the query blocks longest list first, which shortens the
+ * end of the launch when list lengths differ; null = storage order.  Same result either way. */
 int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
                    const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, int kv_rows,
-                   float scale, void* stream);
+                   float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- 64x64 block granularity --------------------------------------------------------------- */
 
@@ -165,8 +167,8 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
                              int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream);
 
-/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs and fgattn_sp_attn_blocks can use (work-queue
- * counter + processing order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
+/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs and fgattn_sp_attn_blocks / fgattn_sp_attn can use
+ * (work-queue counter + processing order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
  * two calls that may overlap on the device must not share it. */
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);
 

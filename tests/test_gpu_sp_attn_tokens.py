@@ -84,3 +84,8 @@ def test_ragged_counts_empty_lists_and_bad_entries():
     capi.sp_attn(o, q.cuda(), k.cuda(), v.cuda(), idx.cuda(), cnt.cuda())
     capi.check()
     _close(o, orc.sp_attn_tokens(q, k, v, idx, cnt, 128))
+    # the order in which the thread blocks take the query blocks changes nothing in the result
+    o_st = torch.full_like(o, float("nan"))
+    capi.sp_attn(o_st, q.cuda(), k.cuda(), v.cuda(), idx.cuda(), cnt.cuda(), ordered=False)
+    capi.check()
+    assert torch.equal(o_st, o)
