@@ -661,7 +661,7 @@ int fgattn_unpack_mask(void* mask, int elem_size, const unsigned char* packed, l
   const long long n_bytes = rows * (width / 8);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (elem_size == 4)
-    fg::unpack_mask_kernel<int><<<byte_grid(n_bytes), 256, 0, st>>>(packed, static_cast<int*>(mask), n_bytes);
+    fg::unpack_mask_kernel<int><<<byte_grid(2 * n_bytes), 256, 0, st>>>(packed, static_cast<int*>(mask), n_bytes);
   else
     fg::unpack_mask_kernel<uint8_t><<<byte_grid(n_bytes), 256, 0, st>>>(packed, static_cast<uint8_t*>(mask), n_bytes);
   FG_CUDA(cudaGetLastError());

@@ -35,17 +35,22 @@ pack_mask_kernel(const T* __restrict__ mask, uint8_t* __restrict__ packed, long 
   }
 }
 
-// packed bytes -> mask of 0 / 1 entries (T = uint8_t or int32); one thread per packed byte.
+// packed bytes -> mask of 0 / 1 entries (T = uint8_t or int32).  int32: one thread per four entries (half
+// a packed byte), so that each store instruction of a warp covers 512 contiguous bytes; uint8: one
+// thread per packed byte (one 8-byte store, 256 contiguous bytes per warp).
 template <typename T>
 __global__ void __launch_bounds__(256)
 unpack_mask_kernel(const uint8_t* __restrict__ packed, T* __restrict__ mask, long long n_bytes) {
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < n_bytes; b += stride) {
-    const uint32_t v = packed[b];
-    if (sizeof(T) == 4) {
-      reinterpret_cast<int4*>(mask)[2 * b] = make_int4(v & 1, (v >> 1) & 1, (v >> 2) & 1, (v >> 3) & 1);
-      reinterpret_cast<int4*>(mask)[2 * b + 1] = make_int4((v >> 4) & 1, (v >> 5) & 1, (v >> 6) & 1, (v >> 7) & 1);
-    } else {
+  const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (sizeof(T) == 4) {
+    for (long long q = t0; q < 2 * n_bytes; q += stride) {          // q = index of a group of four entries
+      const uint32_t v = uint32_t(packed[q >> 1]) >> (4 * int(q & 1));
+      reinterpret_cast<int4*>(mask)[q] = make_int4(v & 1, (v >> 1) & 1, (v >> 2) & 1, (v >> 3) & 1);
+    }
+  } else {
+    for (long long b = t0; b < n_bytes; b += stride) {
+      const uint32_t v = packed[b];
       uint2 o;
       o.x = (v & 1) | (((v >> 1) & 1) << 8) | (((v >> 2) & 1) << 16) | (((v >> 3) & 1) << 24);
       o.y = ((v >> 4) & 1) | (((v >> 5) & 1) << 8) | (((v >> 6) & 1) << 16) | (((v >> 7) & 1) << 24);
