@@ -82,7 +82,8 @@ __device__ __forceinline__ void fill_tail(int* __restrict__ dst, int from, int n
 __global__ void __launch_bounds__(256)
 mask_to_index_kernel(const int* __restrict__ mask, int* __restrict__ idx, int* __restrict__ cnt, int stride,
                      int n_valid) {
-  __shared__ int warp_tot[8];
+  constexpr int kChunks = 4;                 // 1024-column chunks per sweep: four 16-byte loads in flight per thread
+  __shared__ int warp_tot[kChunks][8];
   __shared__ int s_base;
   const size_t rowoff = size_t(blockIdx.x) * stride;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -91,39 +92,63 @@ mask_to_index_kernel(const int* __restrict__ mask, int* __restrict__ idx, int* _
   if (tid == 0) s_base = 0;
   __syncthreads();
   const bool vec = ((stride & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-  for (int c0 = 0; c0 < stride; c0 += 1024) {
-    const int col = c0 + tid * 4;
-    int v[4] = {0, 0, 0, 0};
-    if (vec && col + 3 < stride) {
-      const int4 x = *reinterpret_cast<const int4*>(src + col);
-      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
-    } else {
+  for (int c0 = 0; c0 < stride; c0 += 1024 * kChunks) {
+    int v[kChunks][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (col + e < stride) v[e] = src[col + e];
-    }
-    int f[4], c = 0;
+    for (int k = 0; k < kChunks; ++k) {
+      const int col = c0 + k * 1024 + tid * 4;
+      if (vec && col + 3 < stride) {
+        const int4 x = *reinterpret_cast<const int4*>(src + col);
+        v[k][0] = x.x; v[k][1] = x.y; v[k][2] = x.z; v[k][3] = x.w;
+      } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      f[e] = (v[e] > 0 && col + e < n_valid) ? 1 : 0;
-      c += f[e];
+        for (int e = 0; e < 4; ++e) v[k][e] = (col + e < stride) ? src[col + e] : 0;
+      }
     }
-    int incl = c;
+    uint32_t keep[kChunks];                  // 4 keep bits per chunk
+    int c[kChunks], incl[kChunks];
+#pragma unroll
+    for (int k = 0; k < kChunks; ++k) {
+      const int col = c0 + k * 1024 + tid * 4;
+      keep[k] = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) keep[k] |= (v[k][e] > 0 && col + e < n_valid) ? (1u << e) : 0u;
+      c[k] = __popc(keep[k]);
+      incl[k] = c[k];
+    }
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
+#pragma unroll
+      for (int k = 0; k < kChunks; ++k) {
+        const int n = __shfl_up_sync(0xffffffffu, incl[k], o);
+        if (lane >= o) incl[k] += n;
+      }
     }
-    if (lane == 31) warp_tot[warp] = incl;
+    if (lane == 31) {
+#pragma unroll
+      for (int k = 0; k < kChunks; ++k) warp_tot[k][warp] = incl[k];
+    }
     __syncthreads();
     int off = s_base;
-    for (int w = 0; w < warp; ++w) off += warp_tot[w];
-    off += incl - c;
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      if (f[e]) dst[off++] = col + e;
+    for (int k = 0; k < kChunks; ++k) {
+      int mine = off;                        // start of chunk k
+      int chunk_total = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const int t = warp_tot[k][w];
+        if (w < warp) mine += t;
+        chunk_total += t;
+      }
+      mine += incl[k] - c[k];
+      const int col = c0 + k * 1024 + tid * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if ((keep[k] >> e) & 1u) dst[mine++] = col + e;
+      off += chunk_total;
+    }
     __syncthreads();
-    if (tid == 255) s_base = off;          // last thread's running offset = total so far
+    if (tid == 0) s_base = off;              // every thread holds the same running total
     __syncthreads();
   }
   const int total = s_base;
