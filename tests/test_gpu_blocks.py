@@ -180,3 +180,43 @@ def test_identity_lists_equal_dense():
         capi.check()
         d = (o.float() - dense.float()).abs()
         assert d.max().item() <= 8e-3 and d.mean().item() <= 5e-4, (fn, d.max().item(), d.mean().item())
+
+
+@pytest.mark.parametrize("group", ["1", "2", None])
+def test_thread_block_order_with_several_head_groups(monkeypatch, group):
+    """The longest-first order is built per group of heads (FGATTN_GROUP_HEADS overrides the group size);
+    whatever the grouping, every item must be visited exactly once: same output as storage order."""
+    from oracle import fgattn_oracle as orc
+    capi = _capi()
+    if group is None:
+        monkeypatch.delenv("FGATTN_GROUP_HEADS", raising=False)
+    else:
+        monkeypatch.setenv("FGATTN_GROUP_HEADS", group)
+    B, H, S, D = 1, 5, 1500, 64
+    nqb = nkb = (S + 63) // 64
+    g = torch.Generator().manual_seed(77)
+    q, k, v = (torch.randn(B, H, S, D, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    dens = torch.rand(B, H, nqb, 1, generator=g)                     # list lengths from empty to full
+    bm = torch.rand(B, H, nqb, nkb, generator=g) < dens
+    idx, cnt = orc.bitmask_to_indexmask(bm)
+    idx, cnt = idx.cuda(), cnt.cuda()
+    o_st = torch.full_like(q, float("nan"))
+    o_or = torch.full_like(q, float("nan"))
+    capi.sp_attn_blocks(o_st, q, k, v, idx, cnt, ordered=False)
+    capi.sp_attn_blocks(o_or, q, k, v, idx, cnt)
+    capi.check()
+    assert torch.equal(o_st, o_or)
+    # token lists: the same block lists expanded to tokens, 128-row query blocks
+    nb = (S + 127) // 128
+    tm = bm[:, :, 0::2].repeat_interleave(64, dim=-1)[..., :S]
+    tidx, tcnt = orc.bitmask_to_indexmask(tm)
+    stride = 128 * ((tidx.shape[-1] + 127) // 128)
+    pad = torch.full((B, H, nb, stride), stride, dtype=torch.int32)
+    pad[..., :tidx.shape[-1]] = torch.where(tidx >= S, torch.full_like(tidx, stride), tidx)
+    t_st = torch.full_like(q, float("nan"))
+    t_or = torch.full_like(q, float("nan"))
+    capi.sp_attn(t_st, q, k, v, pad.cuda(), tcnt.cuda(), ordered=False)
+    capi.sp_attn(t_or, q, k, v, pad.cuda(), tcnt.cuda())
+    capi.check()
+    assert torch.equal(t_st, t_or)
+    assert torch.isfinite(t_or.float()).all()
