@@ -340,22 +340,31 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         const int kv_left = p.kv_len - key0;             // valid keys in this tile
         const int valid0 = min(64, kv_left), valid1 = max(0, min(64, kv_left - 64));
         if (MODE == kTokenMask) {
-          // per-token keep bit: any row of the 128-row block with s*c - t_row > log2(tau)
-          const float thr = p.log2_tau + t_row;
+          // per-token keep bit: any row of the 128-row block with s*c - t_row > log2(tau), i.e.
+          // s > thr.  Most 32-column quarters hold no such entry in any row of the warp: their row
+          // maxima settle that with one instruction per entry, and only the others build bits.
+          const float thr = (p.log2_tau + t_row) / c;          // +inf for rows past the sequence
+          uint32_t r[128];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) tmem_ld32(s_addr + w * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[w * 32]));
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));           // the scores are in registers: free the buffer
           uint32_t bits[4];
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
-            uint32_t r[32];
-            tmem_ld32(s_addr + w * 32, r);
-            tmem_ld_wait();
-            uint32_t m = 0;
+            float mx = __uint_as_float(r[w * 32]);
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              m |= (__uint_as_float(r[i]) * c > thr && w * 32 + i < kv_left) ? (1u << i) : 0u;
-            bits[w] = __reduce_or_sync(0xffffffffu, m);
+            for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[w * 32 + i]));
+            bits[w] = 0u;
+            if (__any_sync(0xffffffffu, mx > thr)) {
+              uint32_t m = 0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                m |= (__uint_as_float(r[w * 32 + i]) > thr && w * 32 + i < kv_left) ? (1u << i) : 0u;
+              bits[w] = __reduce_or_sync(0xffffffffu, m);
+            }
           }
-          tc_fence_before();
-          mbar_arrive(bar(BAR_S_EMPTY + t * 2 + b));
           // the caller-zeroed mask is only ever set: four warps (32 rows each) OR into it
           if (q0 + t * 128 < p.S) {
             const int qblk = (q0 + t * 128) >> 7;
