@@ -242,6 +242,13 @@ def main():
     # visits the kept 64x64 blocks
     ms_tokmask = ev_time(lambda: capi.booleanmask_128(tmask, max_q, denom, q, k, w.tau), 3, 1)
     ms_tokmask_listed = ev_time(lambda: capi.booleanmask_128_listed(tmask, max_q, denom, q, k, w.tau, idx, cnt), 5, 2)
+    # the reference's sparse operator on the threshold token lists of that mask (lists of very different lengths)
+    thr_idx = torch.empty_like(tmask)
+    thr_cnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
+    capi.booleanmask_to_indexmask(thr_idx, thr_cnt, tmask, S)
+    ms_tok_thr = ev_time(lambda: capi.sp_attn(o, q, k, v, thr_idx, thr_cnt), 5, 2)
+    F_tok_thr = 4.0 * 128 * D * float(thr_cnt.sum().item())
+    del thr_idx, thr_cnt
     tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
     tpacked = torch.empty(B, H, tmask.shape[2], s_pad // 8, dtype=torch.uint8, device=dev)
     tidx = torch.empty_like(tmask)
@@ -380,6 +387,8 @@ def main():
                 "packedmask_to_indexmask_frac_of_hbm_peak": pack_bytes / ms_p2i / 1e6 / peaks["hbm_gbs"],
                 "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
                 "topk_indices_ms": ms_topk, "topk_select_k": sel_k,
+                "sp_attn_threshold_tokens_ms": ms_tok_thr,
+                "sp_attn_threshold_tokens_tflops_on_listed_tokens": F_tok_thr / ms_tok_thr / 1e9,
                 "sp_attn_tokens_ms": ms_tok, "sp_attn_tokens_tflops_on_listed_tokens": F_tok / ms_tok / 1e9,
                 "sp_attn_blocks_renorm_ms": ms_renorm,
                 "sp_attn_blocks_renorm_tflops_on_kept_blocks": F_sparse / ms_renorm / 1e9,
