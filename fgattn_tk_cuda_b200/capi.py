@@ -31,7 +31,7 @@ PROTOTYPES = {
     "fgattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_booleanmask_128": (_i, [_vp, _f, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_booleanmask_128_listed": (_i, [_vp, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f,
-                                           _vp]),
+                                           _vp, _sz, _vp]),
     "fgattn_booleanmask_to_indexmask": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "fgattn_all_index_mask": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "fgattn_sp_attn": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
@@ -145,14 +145,19 @@ def booleanmask_128(booleanmask, max_q, denom, q, k, threshold, kv_seq_len=None,
 
 
 def booleanmask_128_listed(booleanmask, max_q, denom, q, k, threshold, kb_indices, kb_counts, kv_seq_len=None,
-                           scale=0.0):
-    """booleanmask_128 restricted to the 64x64 blocks that block_index_lists kept for the same inputs."""
+                           scale=0.0, workspace=None, ordered=True):
+    """booleanmask_128 restricted to the 64x64 blocks that block_index_lists kept for the same inputs.
+    ordered: thread blocks take the longest lists first (workspace allocated here when not given)."""
     _check_qkv(q, k)
     B, H, S, D = q.shape
+    if ordered and workspace is None:
+        workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
+    ws_ptr = _ptr(workspace) if ordered else None
+    ws_bytes = workspace.numel() * workspace.element_size() if ordered else 0
     with torch.cuda.device(q.device):
         _call("fgattn_booleanmask_128_listed", _ptr(booleanmask), float(threshold), booleanmask.shape[3], _ptr(max_q),
               _ptr(denom), _ptr(q), _ptr(k), _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3], B, H, S, D,
-              k.shape[2], kv_seq_len or k.shape[2], scale, _stream(q))
+              k.shape[2], kv_seq_len or k.shape[2], scale, ws_ptr, ws_bytes, _stream(q))
 
 
 def booleanmask_to_indexmask(kv_indices, kv_num_indices, booleanmask, seq):

@@ -39,6 +39,7 @@ struct DenseParams {
   const int* kb_idx;
   const int* kb_cnt;
   int list_stride, nqb64;
+  const int* order;     // with lists, optional: thread block i works on item order[i] (longest lists first)
   float scale_log2;     // softmax scale * log2(e)
   float log2_tau;       // kTokenMask
 };
@@ -88,7 +89,8 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * BAR_COUNT + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int first_item = blockIdx.x, item_step = gridDim.x;
+  const int first_item = (MODE == kTokenMask && p.order) ? p.order[blockIdx.x] : int(blockIdx.x);
+  const int item_step = gridDim.x;
 
   if (tid == 0) {
     ab->flag = 0;

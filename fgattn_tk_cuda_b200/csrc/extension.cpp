@@ -96,11 +96,15 @@ void booleanmask_128_listed(torch::Tensor booleanmask, torch::Tensor o_max_q, to
   check_dtype(o_max_q, at::kFloat, "o_max_q"); check_dtype(o_denom, at::kFloat, "o_denom");
   check_dtype(kb_indices, at::kInt, "kb_indices"); check_dtype(kb_counts, at::kInt, "kb_counts");
   c10::cuda::CUDAGuard guard(q.device());
+  // scratch for the longest-first order of the thread blocks, from the stream-ordered caching allocator
+  const int64_t ws_bytes = int64_t(fgattn_sp_attn_workspace_bytes(q.size(0), q.size(1), q.size(2)));
+  torch::Tensor ws = torch::empty({ws_bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
   check_status(fgattn_booleanmask_128_listed(booleanmask.data_ptr<int>(), float(threshold), int(booleanmask.size(3)),
                                              o_max_q.data_ptr<float>(), o_denom.data_ptr<float>(), q.data_ptr(),
                                              k.data_ptr(), kb_indices.data_ptr<int>(), kb_counts.data_ptr<int>(),
                                              int(kb_indices.size(3)), q.size(0), q.size(1), q.size(2), q.size(3),
-                                             k.size(2), k.size(2), 0.f, stream_of(q)), "booleanmask_128_listed");
+                                             k.size(2), k.size(2), 0.f, ws.data_ptr(), size_t(ws_bytes), stream_of(q)),
+               "booleanmask_128_listed");
 }
 
 void booleanmask_to_indexmask(torch::Tensor kv_indices, torch::Tensor kv_numindices, torch::Tensor booleanmask,

@@ -80,11 +80,14 @@ int fgattn_booleanmask_128(int* booleanmask, float threshold, int mask_stride, c
  * same q, k and threshold (kb_indices / kb_counts / list_stride as that call wrote them, max_q / denom
  * from the same call).  A token can only pass the threshold inside a kept block, so the result is the
  * mask of fgattn_booleanmask_128 (up to scores within rounding of the threshold) while the second
- * Q K^T pass of include/mask_utils.cuh:131-243 shrinks to the key tiles that some kept block touches. */
+ * Q K^T pass of include/mask_utils.cuh:131-243 shrinks to the key tiles that some kept block touches.
+ * `workspace` (fgattn_sp_attn_workspace_bytes, scratch) is optional: with it the thread blocks take the
+ * query blocks with the longest lists first; null = storage order.  Same mask either way. */
 int fgattn_booleanmask_128_listed(int* booleanmask, float threshold, int mask_stride, const float* max_q,
                                   const float* denom, const void* q, const void* k, const int* kb_indices,
                                   const int* kb_counts, int list_stride, int batch, int heads, int seq, int D,
-                                  int kv_rows, int kv_seq_len, float scale, void* stream);
+                                  int kv_rows, int kv_seq_len, float scale, void* workspace, size_t workspace_bytes,
+                                  void* stream);
 
 /* Mask rows -> ascending index lists: for every (b,h,seqblock) row of booleanmask
  * ([B,H,seqblocks,mask_stride] int32, > 0 = keep) write the kept columns < seq in ascending order
@@ -167,7 +170,8 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
                              int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream);
 
-/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs and fgattn_sp_attn_blocks / fgattn_sp_attn can use
+/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs and fgattn_sp_attn_blocks / fgattn_sp_attn /
+ * fgattn_booleanmask_128_listed can use
  * (work-queue counter + processing order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
  * two calls that may overlap on the device must not share it. */
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);

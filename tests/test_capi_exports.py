@@ -51,6 +51,10 @@ def test_argument_validation_needs_no_device():
     assert lib.fgattn_maxq_denom(null, null, buf, buf, 1, 1, 64, 64, 64, 64, 0.0, null) == 1
     assert lib.fgattn_booleanmask_to_indexmask(buf, buf, buf, 1, 1, 64, 0, 128, null) == 1
     assert lib.fgattn_sp_attn_blocks_ml(buf, buf, buf, buf, buf, buf, 4, null, null, 1, 1, 64, 64, 64, 64, 0.0, buf, 64, null) == 1
+    assert lib.fgattn_booleanmask_128_listed(buf, 1e-3, 128, buf, buf, buf, buf, null, buf, 4, 1, 1, 64, 64, 64, 64, 0.0,
+                                             null, 0, null) == 1
+    assert lib.fgattn_booleanmask_128_listed(buf, 1e-3, 128, buf, buf, buf, buf, buf, buf, 4, 1, 1, 64, 64, 64, 64, 0.0,
+                                             buf, 8, null) == 7
     assert lib.fgattn_sp_attn(buf, buf, buf, buf, buf, null, 128, 1, 1, 64, 64, 64, 0.0, null, 0, null) == 1
     assert lib.fgattn_sp_attn(buf, buf, buf, buf, buf, buf, 128, 1, 1, 64, 64, 64, 0.0, buf, 8, null) == 7
     assert lib.fgattn_sp_attn_blocks(buf, buf, buf, buf, null, buf, 4, 1, 1, 64, 64, 64, 64, 0.0, null, 0, null) == 1

@@ -126,6 +126,11 @@ def test_token_mask_inside_kept_blocks(S, D, kv):
         assert not (got[..., n_kv:] != 0).any()
     diff = (listed[..., :n_kv].cpu() > 0) ^ (plain[..., :n_kv].cpu() > 0)
     assert not (diff & ~near).any()
+    # thread blocks in storage order instead of longest lists first: the same mask
+    unordered = torch.full_like(listed, 9)
+    capi.booleanmask_128_listed(unordered, m, l, q, k, w.tau, idx, cnt, kv_seq_len=kv, ordered=False)
+    capi.check()
+    assert torch.equal(unordered, listed)
 
 
 @pytest.mark.parametrize("name", GOLDEN_CASES)
