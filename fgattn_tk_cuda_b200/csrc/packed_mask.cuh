@@ -61,11 +61,12 @@ unpack_mask_kernel(const uint8_t* __restrict__ packed, T* __restrict__ mask, lon
 
 // Packed mask row -> ascending index list + count.  Row r of `packed` has row_bytes bytes; entry e is
 // kept iff its bit is set and e < n_valid.  Unused list slots receive `sentinel`.  grid (rows), 256
-// threads; each thread owns one 32-entry word per sweep.
+// threads; each thread owns four 32-entry words per sweep.
 __global__ void __launch_bounds__(256)
 packed_to_index_kernel(const uint8_t* __restrict__ packed, int row_bytes, int* __restrict__ idx, int* __restrict__ cnt,
                        int list_stride, int n_valid, int sentinel) {
-  __shared__ int warp_tot[8];
+  constexpr int kChunks = 4;                 // 256-word chunks per sweep (32768 entries), one pair of barriers per sweep
+  __shared__ int warp_tot[kChunks][8];
   __shared__ int s_base;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint8_t* src = packed + size_t(blockIdx.x) * row_bytes;
@@ -74,41 +75,64 @@ packed_to_index_kernel(const uint8_t* __restrict__ packed, int row_bytes, int* _
   if (tid == 0) s_base = 0;
   __syncthreads();
   const int n_words = (row_bytes + 3) >> 2;
-  for (int w0 = 0; w0 < n_words; w0 += 256) {
-    const int w = w0 + tid;
-    uint32_t bits = 0;
-    if (w < n_words) {
-      if (words) {
-        bits = reinterpret_cast<const uint32_t*>(src)[w];
-      } else {
+  for (int w0 = 0; w0 < n_words; w0 += 256 * kChunks) {
+    uint32_t bits[kChunks];
+    int c[kChunks], incl[kChunks];
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (4 * w + e < row_bytes) bits |= uint32_t(src[4 * w + e]) << (8 * e);
+    for (int k = 0; k < kChunks; ++k) {
+      const int w = w0 + k * 256 + tid;
+      bits[k] = 0;
+      if (w < n_words) {
+        if (words) {
+          bits[k] = reinterpret_cast<const uint32_t*>(src)[w];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (4 * w + e < row_bytes) bits[k] |= uint32_t(src[4 * w + e]) << (8 * e);
+        }
+        const int left = n_valid - 32 * w;               // entries of this word below n_valid
+        if (left <= 0) bits[k] = 0;
+        else if (left < 32) bits[k] &= (1u << left) - 1u;
       }
-      const int left = n_valid - 32 * w;                 // entries of this word below n_valid
-      if (left <= 0) bits = 0;
-      else if (left < 32) bits &= (1u << left) - 1u;
+      c[k] = __popc(bits[k]);
+      incl[k] = c[k];
     }
-    const int c = __popc(bits);
-    int incl = c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
+#pragma unroll
+      for (int k = 0; k < kChunks; ++k) {
+        const int n = __shfl_up_sync(0xffffffffu, incl[k], o);
+        if (lane >= o) incl[k] += n;
+      }
     }
-    if (lane == 31) warp_tot[warp] = incl;
+    if (lane == 31) {
+#pragma unroll
+      for (int k = 0; k < kChunks; ++k) warp_tot[k][warp] = incl[k];
+    }
     __syncthreads();
     int off = s_base;
-    for (int i = 0; i < warp; ++i) off += warp_tot[i];
-    off += incl - c;
-    while (bits) {
-      const int e = __ffs(bits) - 1;
-      bits &= bits - 1;
-      if (off < list_stride) dst[off] = 32 * w + e;
-      ++off;
+#pragma unroll
+    for (int k = 0; k < kChunks; ++k) {
+      int mine = off, chunk_total = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = warp_tot[k][i];
+        if (i < warp) mine += t;
+        chunk_total += t;
+      }
+      mine += incl[k] - c[k];
+      const int w = w0 + k * 256 + tid;
+      uint32_t u = bits[k];
+      while (u) {
+        const int e = __ffs(u) - 1;
+        u &= u - 1;
+        if (mine < list_stride) dst[mine] = 32 * w + e;
+        ++mine;
+      }
+      off += chunk_total;
     }
     __syncthreads();
-    if (tid == 255) s_base = off;
+    if (tid == 0) s_base = off;              // every thread holds the same running total
     __syncthreads();
   }
   const int total = s_base;
