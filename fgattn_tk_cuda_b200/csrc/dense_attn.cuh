@@ -363,17 +363,19 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               uint32_t m = 0;
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                m |= (__uint_as_float(r[w * 32 + i]) > thr && w * 32 + i < kv_left) ? (1u << i) : 0u;
+                if (__uint_as_float(r[w * 32 + i]) > thr) m |= 1u << i;
+              const int lim = kv_left - w * 32;                  // live columns of this quarter
+              m &= (lim >= 32) ? 0xffffffffu : (lim <= 0 ? 0u : ((1u << lim) - 1u));
               bits[w] = __reduce_or_sync(0xffffffffu, m);
             }
           }
-          // the caller-zeroed mask is only ever set: four warps (32 rows each) OR into it
+          // the caller-zeroed mask is only ever set to 1 (by up to four warps of 32 rows each)
           if (q0 + t * 128 < p.S) {
             const int qblk = (q0 + t * 128) >> 7;
             int* mrow = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + qblk) * p.mask_stride + key0;
 #pragma unroll
             for (int w = 0; w < 4; ++w)
-              if ((bits[w] >> lane) & 1u) atomicOr(mrow + w * 32 + lane, 1);
+              if ((bits[w] >> lane) & 1u) mrow[w * 32 + lane] = 1;
           }
           continue;
         }
