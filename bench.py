@@ -8,13 +8,21 @@ Metric: TFLOP/s on kept 64x64 blocks (4*64*64*D flops per kept block).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--impl reference]
 
-For N > 1 launch under `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N`;
-every rank runs the full workload on its own heads (weak scaling, no collective on the data path).
-Rank 0 prints one JSON line.
+For N > 1 launch under `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N`.
+The headline is weak scaling: every rank runs the whole workload on its own head seeds, no collective
+on the data path.  Next to it the line carries, under "strong", ONE fixed workload (C3, and the
+long-context C5) whose (batch x head) units are divided over the ranks, and the cost of gathering the
+outputs with NCCL afterwards.  Rank 0 prints one JSON line.
+
+The "e2e" number starts from q, k, v in pinned host memory and does the same work as the reference
+arm's CPU step: build the threshold block lists AND run the sparse attention, outputs read back to the
+host -- every step.  "e2e_cached_lists" is the sparse operator alone on host buffers (lists built once).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
+import dataclasses
 import json
 import os
 import sys
@@ -29,6 +37,9 @@ import torch  # noqa: E402
 
 METRIC = "sparse_fwd_tflops_on_kept_blocks"
 UNIT = "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_ml_persistent_kernel<128> launch over the
+# first 16 heads of C3 (one ncu capture); the traffic grows in proportion to the heads of a launch
+NCU_DRAM_BYTES_PER_C3_HEAD = 312.0e6 / 16.0
 
 
 def read_peaks():
@@ -41,9 +52,9 @@ def read_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML while a timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.004):
+    def __init__(self, index: int, period_s: float = 0.001):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -111,16 +122,13 @@ def cpu_sample(workload, rows: int):
 
 
 def cpu_step(q_rows, k, v, tau):
-    """The reference's CPU path for the sparse step on the sample: softmax over all keys, 64x64
-    threshold block map, masked P*V without renormalisation (python/spattn/mask_utils.py:206-245,
+    """The reference's CPU path for one step on the sample: softmax over all keys, 64x64 threshold
+    block map, masked P*V without renormalisation (python/spattn/mask_utils.py:206-245,
     python/test_mask.py:37-54), through the oracle port.  Returns kept blocks."""
     from oracle import fgattn_oracle as orc
     S_kv = k.shape[2]
-    kk = k
-    # the oracle functions take q and k of equal length only for shape bookkeeping of m/l; the
-    # block map and the masked attention work on any number of query rows
-    bm = orc.qk_block_bitmask(q_rows, kk, tau, 64, 64, kv_seq_len=S_kv)
-    orc.block_masked_attn(q_rows, kk, v, bm, 64, 64, kv_seq_len=S_kv)
+    bm = orc.qk_block_bitmask(q_rows, k, tau, 64, 64, kv_seq_len=S_kv)
+    orc.block_masked_attn(q_rows, k, v, bm, 64, 64, kv_seq_len=S_kv)
     return int(bm.sum())
 
 
@@ -130,6 +138,7 @@ def run_cpu(workload, steps: int, warmup: int, budget_s: float):
     D = workload.D
     # calibrate the sample size (query rows) against the time budget
     q, k, v = cpu_sample(workload, 256)
+    cpu_step(q, k, v, workload.tau)                       # first call pays one-off set-up
     t0 = time.perf_counter()
     cpu_step(q, k, v, workload.tau)
     t256 = time.perf_counter() - t0
@@ -147,8 +156,123 @@ def run_cpu(workload, steps: int, warmup: int, budget_s: float):
     flops = 4.0 * 64 * 64 * D * kept
     return {"value": flops / mean_s / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"head 0 of {workload.name}, first {rows} query rows x all {workload.S} keys, fp32 torch CPU: "
-                      f"threshold block map + masked attention; {mean_s:.2f} s per step, {kept} kept blocks",
+                      f"threshold block map + masked attention (the work of the GPU arm's e2e step); "
+                      f"{mean_s:.2f} s per step, {kept} kept blocks",
             "ms_per_step": mean_s * 1e3}
+
+
+# --------------------------------------------------------------------------------------------------
+# helpers of the GPU arm
+# --------------------------------------------------------------------------------------------------
+def ev_time(fn, n, warm, flush=None):
+    """Mean device time of fn() in ms (CUDA events on the current stream).  With `flush` (a buffer
+    larger than L2) every timed call is preceded by a write of that buffer and timed on its own."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+    tot = 0.0
+    for _ in range(n):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    return tot / n
+
+
+def timed_region(step, n, sampler_index):
+    """n back-to-back steps between two events, SM clock sampled meanwhile."""
+    torch.cuda.synchronize()
+    sampler = ClockSampler(sampler_index)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n, sampler.stop()
+
+
+def union_overhead(idx, cnt, nkb):
+    """Block products the sparse kernel issues per kept block.  A work item walks the sorted union
+    of the lists of two neighbouring 64-row query blocks on one 128-row tile, two key blocks per
+    step, so it computes 2 x 2 x ceil(|union| / 2) block products where the lists hold n0 + n1."""
+    live = torch.arange(idx.shape[3], device=idx.device)[None, None, None, :] < cnt[..., None]
+    bm = torch.zeros(*idx.shape[:3], nkb + 1, dtype=torch.bool, device=idx.device)
+    bm.scatter_(3, torch.where(live, idx.long(), torch.full_like(idx, nkb).long()), True)
+    bm = bm[..., :nkb]
+    if bm.shape[2] & 1:
+        bm = torch.cat([bm, torch.zeros_like(bm[:, :, :1])], dim=2)
+    u = (bm[:, :, 0::2] | bm[:, :, 1::2]).sum(-1)
+    steps = (u + 1) // 2
+    return 4.0 * float(steps.sum().item()) / max(1.0, float(cnt.sum().item()))
+
+
+def host_buffer(nbytes: int, write_combined: bool):
+    """Pinned host memory as a uint8 tensor.  write_combined: cudaHostAllocWriteCombined, which the
+    device reads without snooping the CPU caches (good for buffers the host only writes)."""
+    if write_combined:
+        try:
+            rt = ctypes.CDLL("libcudart.so.12")
+            p = ctypes.c_void_p()
+            if rt.cudaHostAlloc(ctypes.byref(p), ctypes.c_size_t(nbytes), ctypes.c_uint(0x04)) == 0 and p.value:
+                buf = (ctypes.c_uint8 * nbytes).from_address(p.value)
+                t = torch.frombuffer(buf, dtype=torch.uint8)
+                if t.is_pinned():
+                    return t, "cudaHostAlloc write-combined"
+        except Exception:
+            pass
+    return torch.empty(nbytes, dtype=torch.uint8).pin_memory(), "pinned (torch pin_memory)"
+
+
+def run_shard(w, units, dev, chunk_units, steps, warm, keep_output=False):
+    """Lists + sparse pass over the global (batch x head) units `units` of workload w, processed in
+    chunks of at most chunk_units units (each chunk = one launch of every kernel).  Device times are
+    summed over the chunks."""
+    from fgattn_tk_cuda_b200 import capi, synth
+    S, D = w.S, w.D
+    nqb = nkb = (S + 63) // 64
+    s_pad = 128 * ((S + 127) // 128)
+    ms_lists = ms_sparse = 0.0
+    nnz = 0
+    outs = []
+    units = list(units)
+    scratch = None
+    for c0 in range(0, len(units), chunk_units):
+        chunk = units[c0:c0 + chunk_units]
+        n = len(chunk)
+        q, k, v = synth.make_qkv(w, device=dev, heads=chunk)
+        idx = torch.empty(1, n, nqb, nkb, dtype=torch.int32, device=dev)
+        cnt = torch.empty(1, n, nqb, dtype=torch.int32, device=dev)
+        m = torch.empty(1, n, 1, s_pad, device=dev)
+        l = torch.empty_like(m)
+        o = torch.empty_like(q)
+        if scratch is None:
+            per_unit = capi.block_scratch_bytes(1, 1, S)
+            scratch = torch.empty(min(n, max(1, (4 << 30) // per_unit)) * per_unit // 4, device=dev)
+        ws = torch.empty(capi.sp_attn_workspace_bytes(1, n, S), dtype=torch.uint8, device=dev)
+        ms_lists += ev_time(lambda: capi.block_index_lists(idx, cnt, m, l, q, k, w.tau, scratch), 1, 1)
+        ms_sparse += ev_time(lambda: capi.sp_attn_blocks_ml(o, q, k, v, idx, cnt, m, l, workspace=ws), steps, warm)
+        nnz += int(cnt.sum().item())
+        if keep_output:
+            outs.append(o[0])
+        del q, k, v, idx, cnt, m, l
+        if not keep_output:
+            del o
+    capi.check()
+    return {"ms_lists": ms_lists, "ms_sparse": ms_sparse, "nnz": nnz, "units": len(units),
+            "out": torch.cat(outs, 0) if keep_output and outs else None}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -160,15 +284,20 @@ def main():
     ap.add_argument("--workload", default="c3")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--heads", type=int, default=0, help="profile-sized run: only the first N heads (B=1)")
+    ap.add_argument("--heads", type=int, default=0, help="profile-sized run: only the first N heads (B=1), "
+                    "headline and stage timings only")
+    ap.add_argument("--sections", default="", help="comma list out of stages,e2e,strong,configs "
+                    "(default: all; with --heads: stages,e2e)")
+    ap.add_argument("--host-wc", type=int, default=1, help="1: write-combined pinned memory for the host q,k,v")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     from fgattn_tk_cuda_b200 import synth
     w = synth.WORKLOADS[args.workload]
     if args.heads > 0:
-        import dataclasses
         w = dataclasses.replace(w, name=f"{w.name}_first{args.heads}heads", B=1, H=args.heads)
+    sections = set(s for s in args.sections.split(",") if s) or (
+        {"stages", "e2e"} if args.heads > 0 or args.workload != "c3" else {"stages", "e2e", "strong", "configs"})
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -179,12 +308,13 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        steps = min(args.steps, 20)
-        r = run_cpu(w, steps, min(args.warmup, 3), budget_s=150.0)
+        r = run_cpu(w, args.steps, args.warmup, budget_s=150.0)
         line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
-                "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": r["ms_per_step"],
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": config,
+                "work_per_step": "threshold block map + masked attention on the sample (what the GPU arm's e2e step "
+                                 "does for the whole workload); credited with the kept-block flops only",
                 "cpu_baseline": {k_: r[k_] for k_ in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -192,35 +322,32 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
-    from fgattn_tk_cuda_b200 import capi
+    from fgattn_tk_cuda_b200 import capi, sharded
     import fgattn_tk_cuda_b200.spattn as spattn            # registers torch.ops.cuda_attn (the plugin boundary)
+    ops = torch.ops.cuda_attn
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    gpu_index = physical_gpu_index(local_rank)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
     peaks = read_peaks()
+    peak = peaks["bf16_tflops"]
     n_heads = w.B * w.H
     heads = range(rank * n_heads, (rank + 1) * n_heads)    # disjoint seeds per rank, same shapes
     q, k, v = synth.make_qkv(w, device=dev, heads=heads)
     q, k, v = (t.view(w.B, w.H, w.S, w.D) for t in (q, k, v))
     B, H, S, D = q.shape
     nqb = nkb = (S + 63) // 64
+    s_pad = 128 * ((S + 127) // 128)
 
-    # ---- untimed set-up: one-pass m/l + lists (+ dense output), timed separately for the report
-    def ev_time(fn, n, warm):
-        for _ in range(warm):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / n
-
+    # ---- untimed set-up: one-pass m/l + lists
     o = torch.empty_like(q)
     idx, cnt, max_q, denom = spattn.mask_utils.qk_block_indexmask_cuda(q, k, w.tau)
     capi.check()
@@ -228,179 +355,341 @@ def main():
     density = nnz / (B * H * nqb * nkb)
     F_sparse = 4.0 * 64 * 64 * D * nnz
     F_full = 4.0 * B * H * S * S * D
+    u_over = union_overhead(idx, cnt, nkb)
     scratch = spattn.mask_utils._block_scratch(q)
-    ms_full = ev_time(lambda: capi.full_attn(o, q, k, v), 5, 2)
-    ms_lists = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch), 5, 2)
-    ms_maxq = ev_time(lambda: capi.maxq_denom(max_q, denom, q, k), 5, 2)
-    s_pad = 128 * ((S + 127) // 128)
-    mask_bytes = B * H * (4.0 * s_pad * nkb * 2 + 8.0 * S + 4.0 * nqb * nkb + 4.0 * nqb)
-    ms_build = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch, o=o, v=v), 5, 2)
-    # one-bit-per-entry mask kernels on a token mask of the reference granularity (int32 [B,H,S/128,S_pad],
-    # 8 % kept): pack = 4 B read + 1/8 B written per entry; packed -> lists = 1/8 B read + 4 B written
-    tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
-    # threshold token mask (reference granularity): the full second Q K^T pass against the pass that only
-    # visits the kept 64x64 blocks
-    ms_tokmask = ev_time(lambda: capi.booleanmask_128(tmask, max_q, denom, q, k, w.tau), 3, 1)
-    ms_tokmask_listed = ev_time(lambda: capi.booleanmask_128_listed(tmask, max_q, denom, q, k, w.tau, idx, cnt), 5, 2)
-    # the reference's sparse operator on the threshold token lists of that mask (lists of very different lengths)
-    thr_idx = torch.empty_like(tmask)
-    thr_cnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
-    capi.booleanmask_to_indexmask(thr_idx, thr_cnt, tmask, S)
-    ms_tok_thr = ev_time(lambda: capi.sp_attn(o, q, k, v, thr_idx, thr_cnt), 5, 2)
-    F_tok_thr = 4.0 * 128 * D * float(thr_cnt.sum().item())
-    del thr_idx, thr_cnt
-    tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
-    tpacked = torch.empty(B, H, tmask.shape[2], s_pad // 8, dtype=torch.uint8, device=dev)
-    tidx = torch.empty_like(tmask)
-    tcnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
-    pack_bytes = tmask.numel() * (4.0 + 0.125)
-    ms_pack = ev_time(lambda: capi.pack_mask(tpacked, tmask), 10, 3)
-    ms_p2i = ev_time(lambda: capi.packedmask_to_indexmask(tidx, tcnt, tpacked, S), 10, 3)
-    ms_m2i = ev_time(lambda: capi.booleanmask_to_indexmask(tidx, tcnt, tmask, S), 10, 3)
-    del tmask, tidx
-    # top-k selector at the reference granularity: 128-row query blocks, 10 % of the keys
-    sel_k = max(1, S // 10)
-    kstride = 128 * ((sel_k + 127) // 128)
-    kidx = torch.empty(B, H, (S + 127) // 128, kstride, dtype=torch.int32, device=dev)
-    tk_scratch = torch.empty(capi.topk_scratch_bytes(B, H, S, D, 128), dtype=torch.uint8, device=dev)
-    ms_topk = ev_time(lambda: capi.topk_indices(kidx, tcnt, q, k, sel_k, blocksz=128, scratch=tk_scratch), 5, 2)
-    # the reference's own sparse operator (128-row query blocks, key-token lists, renormalising) on those lists
-    ms_tok = ev_time(lambda: capi.sp_attn(o, q, k, v, kidx, tcnt), 5, 2)
-    F_tok = 4.0 * B * H * S * sel_k * D
-    del kidx, tk_scratch
-    # replay of a cached mask: the renormalising block kernel on the same key-block lists
-    ms_renorm = ev_time(lambda: torch.ops.cuda_attn.sp_attn_blocks(o, q, k, v, idx, cnt), 10, 3)
 
-    step = lambda: torch.ops.cuda_attn.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
+    stages = {}
+    if "stages" in sections:
+        ms_full = ev_time(lambda: capi.full_attn(o, q, k, v), 5, 2)
+        ms_lists = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch), 5, 2)
+        ms_maxq = ev_time(lambda: capi.maxq_denom(max_q, denom, q, k), 5, 2)
+        mask_bytes = B * H * (4.0 * s_pad * nkb * 2 + 8.0 * S + 4.0 * nqb * nkb + 4.0 * nqb)
+        ms_build = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch, o=o, v=v), 5, 2)
+        # threshold token mask (reference granularity): the full second Q K^T pass against the pass that only
+        # visits the kept 64x64 blocks
+        tmask = torch.empty(B, H, (S + 127) // 128, s_pad, dtype=torch.int32, device=dev)
+        ms_tokmask = ev_time(lambda: capi.booleanmask_128(tmask, max_q, denom, q, k, w.tau), 3, 1)
+        ms_tokmask_listed = ev_time(lambda: capi.booleanmask_128_listed(tmask, max_q, denom, q, k, w.tau, idx, cnt), 5, 2)
+        # the reference's sparse operator on the threshold token lists of that mask (lists of very different lengths)
+        thr_idx = torch.empty_like(tmask)
+        thr_cnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
+        capi.booleanmask_to_indexmask(thr_idx, thr_cnt, tmask, S)
+        ms_tok_thr = ev_time(lambda: capi.sp_attn(o, q, k, v, thr_idx, thr_cnt), 5, 2)
+        F_tok_thr = 4.0 * 128 * D * float(thr_cnt.sum().item())
+        del thr_idx, thr_cnt
+        # one-bit-per-entry mask kernels on a token mask of the reference granularity (int32 [B,H,S/128,S_pad],
+        # 8 % kept): pack = 4 B read + 1/8 B written per entry; packed -> lists = 1/8 B read + 4 B written
+        tmask = (torch.rand(B, H, (S + 127) // 128, s_pad, device=dev) < 0.08).to(torch.int32)
+        tpacked = torch.empty(B, H, tmask.shape[2], s_pad // 8, dtype=torch.uint8, device=dev)
+        tidx = torch.empty_like(tmask)
+        tcnt = torch.empty(tmask.shape[:3], dtype=torch.int32, device=dev)
+        pack_bytes = tmask.numel() * (4.0 + 0.125)
+        ms_pack = ev_time(lambda: capi.pack_mask(tpacked, tmask), 10, 3)
+        ms_p2i = ev_time(lambda: capi.packedmask_to_indexmask(tidx, tcnt, tpacked, S), 10, 3)
+        ms_m2i = ev_time(lambda: capi.booleanmask_to_indexmask(tidx, tcnt, tmask, S), 10, 3)
+        del tmask, tidx, tpacked
+        # top-k selector at the reference granularity: 128-row query blocks, 10 % of the keys
+        sel_k = max(1, S // 10)
+        kstride = 128 * ((sel_k + 127) // 128)
+        kidx = torch.empty(B, H, (S + 127) // 128, kstride, dtype=torch.int32, device=dev)
+        tk_scratch = torch.empty(capi.topk_scratch_bytes(B, H, S, D, 128), dtype=torch.uint8, device=dev)
+        ms_topk = ev_time(lambda: capi.topk_indices(kidx, tcnt, q, k, sel_k, blocksz=128, scratch=tk_scratch), 5, 2)
+        # the reference's own sparse operator (128-row query blocks, key-token lists, renormalising) on those lists
+        ms_tok = ev_time(lambda: capi.sp_attn(o, q, k, v, kidx, tcnt), 5, 2)
+        F_tok = 4.0 * B * H * S * sel_k * D
+        del kidx, tk_scratch, tcnt
+        # replay of a cached mask: the renormalising block kernel on the same key-block lists
+        ms_renorm = ev_time(lambda: ops.sp_attn_blocks(o, q, k, v, idx, cnt), 10, 3)
+        stages = {
+            "full_attn_ms": ms_full, "full_attn_tflops": F_full / ms_full / 1e9,
+            "full_attn_frac_of_peak": F_full / ms_full / 1e9 / peak,
+            "block_lists_ms": ms_lists, "block_lists_qk_tflops": F_full / 2 / ms_lists / 1e9,
+            "maxq_denom_ms": ms_maxq, "maxq_denom_qk_tflops": F_full / 2 / ms_maxq / 1e9,
+            "mask_epilogue_note": "block_lists_ms - maxq_denom_ms (difference of two timings)",
+            "mask_epilogue_ms": ms_lists - ms_maxq,
+            "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
+            "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
+            "booleanmask_128_ms": ms_tokmask, "booleanmask_128_listed_ms": ms_tokmask_listed,
+            "pack_mask_ms": ms_pack, "pack_mask_gbs": pack_bytes / ms_pack / 1e6,
+            "pack_mask_frac_of_hbm_peak": pack_bytes / ms_pack / 1e6 / peaks["hbm_gbs"],
+            "packedmask_to_indexmask_ms": ms_p2i, "packedmask_to_indexmask_gbs": pack_bytes / ms_p2i / 1e6,
+            "packedmask_to_indexmask_frac_of_hbm_peak": pack_bytes / ms_p2i / 1e6 / peaks["hbm_gbs"],
+            "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
+            "topk_indices_ms": ms_topk, "topk_select_k": sel_k,
+            "sp_attn_threshold_tokens_ms": ms_tok_thr,
+            "sp_attn_threshold_tokens_tflops_on_listed_tokens": F_tok_thr / ms_tok_thr / 1e9,
+            "sp_attn_tokens_ms": ms_tok, "sp_attn_tokens_tflops_on_listed_tokens": F_tok / ms_tok / 1e9,
+            "sp_attn_blocks_renorm_ms": ms_renorm,
+            "sp_attn_blocks_renorm_tflops_on_kept_blocks": F_sparse / ms_renorm / 1e9,
+            "sp_attn_blocks_renorm_frac_of_peak": F_sparse / ms_renorm / 1e9 / peak,
+            "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
+        }
+        # re-build the lists that the stage timings overwrote with equal content (same inputs)
+        capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch)
 
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
+    # ---- the timed region: exactly K steps after W warm-up steps, barrier + synchronize on both sides
+    step = lambda: ops.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
+    ms_step, clocks = timed_region(step, args.steps, gpu_index)
     barrier()
-    clocks = sampler.stop()
     capi.check()
-    ms_step = e0.elapsed_time(e1) / args.steps
+    # the same step 200 times back to back (power cap territory), and a 20-step burst, each with its clock
+    ms_200, clocks_200 = timed_region(step, 200, gpu_index)
+    time.sleep(0.5)
+    for _ in range(3):
+        step()
+    ms_burst, clocks_burst = timed_region(step, 20, gpu_index)
+    if stages:
+        stages.update({"sparse_ms": ms_step, "sparse_speedup_over_full": stages["full_attn_ms"] / ms_step,
+                       "ideal_speedup_1_over_density": 1.0 / density,
+                       "speedup_gap": (1.0 / density) / (stages["full_attn_ms"] / ms_step)})
 
     # ---- end to end through the operator boundary with host buffers
-    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
-    ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
-    # Every step copies its own q, k, v from pinned host memory, runs the operator and reads o back.
-    # Steps are independent, so they are double-buffered over three streams: the copies of step i+1
-    # and the read-back of step i-1 overlap the kernel of step i (H2D and D2H use different engines).
-    cur = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    dbuf = [tuple(torch.empty_like(t) for t in (q, k, v, o)) for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_comp = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+    e2e = {}
+    if "e2e" in sections:
+        nb = q.numel() * q.element_size()
+        hin, host_kind = host_buffer(3 * nb, bool(args.host_wc))
+        hin.view(torch.bfloat16).view(3, *q.shape).copy_(torch.stack([q, k, v]).cpu())
+        ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
+        # Every step copies its own q, k, v from pinned host memory (one copy of the three tensors, which sit
+        # back to back on both sides), runs the operators and reads o back.  Steps are independent, so they
+        # are double-buffered over three streams: the copy-in of step i+1 and the read-back of step i-1
+        # overlap the kernels of step i (H2D and D2H use different engines).
+        cur = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        dbuf = []
+        for _ in range(2):
+            qkv = torch.empty(3, *q.shape, dtype=q.dtype, device=dev)
+            dbuf.append({"qkv": qkv, "o": torch.empty_like(o), "idx": torch.empty_like(idx), "cnt": torch.empty_like(cnt),
+                         "m": torch.empty_like(max_q), "l": torch.empty_like(denom)})
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_comp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    def e2e_step(i):
-        b = i & 1
-        bq, bk, bv, bo = dbuf[b]
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(ev_comp[b])                 # the kernel of step i-2 has read this buffer
-            bq.copy_(hq, non_blocking=True)
-            bk.copy_(hk, non_blocking=True)
-            bv.copy_(hv, non_blocking=True)
-            ev_in[b].record(s_in)
-        cur.wait_event(ev_in[b])
-        cur.wait_event(ev_out[b])                       # o of step i-2 has been read back
-        torch.ops.cuda_attn.sp_attn_blocks_ml(bo, bq, bk, bv, idx, cnt, max_q, denom)
-        ev_comp[b].record(cur)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(ev_comp[b])
-            ho.copy_(bo, non_blocking=True)
-            ev_out[b].record(s_out)
+        def e2e_step(i, mode):
+            b = dbuf[i & 1]
+            j = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_comp[j])                 # the kernels of step i-2 have read this buffer
+                b["qkv"].view(torch.uint8).view(-1).copy_(hin, non_blocking=True)
+                ev_in[j].record(s_in)
+            cur.wait_event(ev_in[j])
+            cur.wait_event(ev_out[j])                       # o of step i-2 has been read back
+            bq, bk, bv = b["qkv"][0], b["qkv"][1], b["qkv"][2]
+            if mode == "full":                              # lists from this step's q, k, then the sparse pass
+                ops.block_index_lists(b["idx"], b["cnt"], b["m"], b["l"], None, bq, bk, None, w.tau, scratch)
+                ops.sp_attn_blocks_ml(b["o"], bq, bk, bv, b["idx"], b["cnt"], b["m"], b["l"])
+            elif mode == "cached":                          # lists and max_q / denom built once, outside
+                ops.sp_attn_blocks_ml(b["o"], bq, bk, bv, idx, cnt, max_q, denom)
+            ev_comp[j].record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_comp[j])
+                ho.copy_(b["o"], non_blocking=True)
+                ev_out[j].record(s_out)
 
-    def e2e_run(n):
+        def e2e_run(n, mode):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(cur)
+            for i in range(n):
+                e2e_step(i, mode)
+            cur.wait_stream(s_in)
+            cur.wait_stream(s_out)
+            e1.record(cur)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        e2e_steps = max(4, min(args.steps, 10))
+        for mode in ("full", "cached", "copies"):
+            e2e_run(2, mode)
+        barrier()
+        e2e["full_ms"] = e2e_run(e2e_steps, "full")
+        barrier()
+        e2e["cached_ms"] = e2e_run(e2e_steps, "cached")
+        barrier()
+        e2e["copies_ms"] = e2e_run(e2e_steps, "copies")
+        capi.check()
+        # the e2e output is the output of the resident-input path
+        ops.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(cur)
-        for i in range(n):
-            e2e_step(i)
-        cur.wait_stream(s_in)
-        cur.wait_stream(s_out)
-        e1.record(cur)
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / n
+        e2e["output_matches_resident_path"] = bool(torch.equal(ho, o.cpu()))
+        e2e["h2d"] = 3 * nb
+        e2e["d2h"] = ho.numel() * ho.element_size()
+        e2e["host_kind"] = host_kind
+        del dbuf, hin, ho
 
-    e2e_steps = max(4, min(args.steps, 10))
-    e2e_run(2)
-    ms_e2e = e2e_run(e2e_steps)
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
-    d2h = ho.numel() * ho.element_size()
+    # ---- one fixed workload divided over the ranks (strong), and the all-gather of its outputs
+    strong = {}
+    if "strong" in sections:
+        c3 = synth.WORKLOADS["c3"]
+        units = synth.shard_heads(c3.B * c3.H, world, rank)
+        barrier()
+        r3 = run_shard(c3, units, dev, 64, 20, 3, keep_output=world > 1)
+        t = torch.tensor([r3["ms_sparse"], r3["ms_lists"]], device=dev, dtype=torch.float64)
+        tot = torch.tensor([float(r3["nnz"])], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        strong["c3"] = {"units_total": c3.B * c3.H, "units_this_rank": len(units), "sparse_ms": t[0].item(),
+                        "lists_ms": t[1].item(), "kept_blocks": int(tot[0].item()),
+                        "sparse_tflops_on_kept_blocks": 4.0 * 64 * 64 * c3.D * tot[0].item() / t[0].item() / 1e9,
+                        "t1_sparse_ms": ms_burst if args.workload == "c3" else None,
+                        "t1_note": "rank 0's own 20-step burst of the whole workload (its weak-scaling seeds are "
+                                   "the canonical heads 0..31)"}
+        if strong["c3"]["t1_sparse_ms"]:
+            strong["c3"]["efficiency"] = strong["c3"]["t1_sparse_ms"] / (world * t[0].item())
+        if world > 1:
+            # gather the shard outputs on every rank with NCCL: never part of the metric
+            total_units = c3.B * c3.H
+            local_o = r3["out"]
+            full = sharded.all_gather_units(local_o, total_units)
+            torch.cuda.synchronize()
+            ok = bool(torch.equal(full[units.start:units.stop], local_o))
+            chk = local_o.view(torch.int16).to(torch.int64).sum().reshape(1)
+            dist.all_reduce(chk, op=dist.ReduceOp.SUM)
+            ok = ok and int(chk.item()) == int(full.view(torch.int16).to(torch.int64).sum().item())
+            del full
+            barrier()
+            ms_ag = ev_time(lambda: sharded.all_gather_units(local_o, total_units), 3, 1)
+            tg = torch.tensor([ms_ag], device=dev, dtype=torch.float64)
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+            out_bytes = total_units * c3.S * c3.D * 2
+            strong["allgather_outputs"] = {"ms": tg[0].item(), "bytes_gathered_per_rank": out_bytes,
+                                           "bus_gbs": out_bytes * (world - 1) / world / tg[0].item() / 1e6,
+                                           "verified": ok, "backend": "nccl all_gather_into_tensor"}
+            del local_o
+        r3["out"] = None
+        # long-context configuration: 512 units of S = 65536, at most 64 per launch
+        c5 = synth.WORKLOADS["c5"]
+        units5 = synth.shard_heads(c5.B * c5.H, world, rank)
+        barrier()
+        r5 = run_shard(c5, units5, dev, 64, 2, 1)
+        t = torch.tensor([r5["ms_sparse"], r5["ms_lists"]], device=dev, dtype=torch.float64)
+        tot = torch.tensor([float(r5["nnz"])], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        nqb5 = c5.S // 64
+        strong["c5"] = {"units_total": c5.B * c5.H, "units_this_rank": len(units5), "sparse_ms": t[0].item(),
+                        "lists_ms": t[1].item(), "kept_blocks": int(tot[0].item()),
+                        "density": tot[0].item() / (c5.B * c5.H * nqb5 * nqb5),
+                        "sparse_tflops_on_kept_blocks": 4.0 * 64 * 64 * c5.D * tot[0].item() / t[0].item() / 1e9,
+                        "lists_qk_tflops": 2.0 * c5.B * c5.H * c5.S * c5.S * c5.D / t[1].item() / 1e9}
+        if world > 1:
+            # the whole workload on rank 0 alone, in the same run, for the efficiency
+            t1 = torch.zeros(2, device=dev, dtype=torch.float64)
+            if rank == 0:
+                r1 = run_shard(c5, range(c5.B * c5.H), dev, 64, 2, 1)
+                t1[0], t1[1] = r1["ms_sparse"], r1["ms_lists"]
+            dist.all_reduce(t1, op=dist.ReduceOp.MAX)
+            strong["c5"].update({"t1_sparse_ms": t1[0].item(), "t1_lists_ms": t1[1].item(),
+                                 "efficiency": t1[0].item() / (world * strong["c5"]["sparse_ms"]),
+                                 "lists_efficiency": t1[1].item() / (world * strong["c5"]["lists_ms"])})
+        else:
+            strong["c5"].update({"t1_sparse_ms": strong["c5"]["sparse_ms"], "t1_lists_ms": strong["c5"]["lists_ms"],
+                                 "efficiency": 1.0, "lists_efficiency": 1.0})
 
-    # ---- max over ranks
-    ms_all, ms_e2e_all, F_total = ms_step, ms_e2e, F_sparse
+    # ---- the other single-GPU configurations (rank 0 only): dense C2, ragged C4
+    configs = {}
+    if "configs" in sections and rank == 0:
+        del q, k, v, o
+        torch.cuda.empty_cache()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)       # larger than L2
+        c2 = synth.WORKLOADS["c2"]
+        q2, k2, v2 = synth.make_qkv(c2, device=dev)
+        o2 = torch.empty_like(q2)
+        ms = ev_time(lambda: capi.full_attn(o2, q2, k2, v2), 10, 3, flush=flush)
+        F2 = 4.0 * c2.B * c2.H * c2.S * c2.S * c2.D
+        configs["c2_dense"] = {"workload": c2.name, "full_attn_ms": ms, "full_attn_tflops": F2 / ms / 1e9,
+                               "full_attn_frac_of_peak": F2 / ms / 1e9 / peak,
+                               "l2": "64 MiB of q,k,v,o: a 256 MiB buffer is written before every timed call"}
+        del q2, k2, v2, o2
+        c4 = synth.WORKLOADS["c4"]
+        q4, k4, v4 = synth.make_qkv(c4, device=dev)
+        o4 = torch.empty_like(q4)
+        i4, n4, m4, l4 = spattn.mask_utils.qk_block_indexmask_cuda(q4, k4, c4.tau)
+        nnz4 = int(n4.sum().item())
+        nb4 = (c4.S + 63) // 64
+        sc4 = spattn.mask_utils._block_scratch(q4)
+        F4 = 4.0 * c4.B * c4.H * c4.S * c4.S * c4.D
+        Fs4 = 4.0 * 64 * 64 * c4.D * nnz4
+        ms_f = ev_time(lambda: capi.full_attn(o4, q4, k4, v4), 5, 2)
+        ms_l = ev_time(lambda: capi.block_index_lists(i4, n4, m4, l4, q4, k4, c4.tau, sc4), 5, 2)
+        ms_s = ev_time(lambda: ops.sp_attn_blocks_ml(o4, q4, k4, v4, i4, n4, m4, l4), 20, 3)
+        ms_r = ev_time(lambda: ops.sp_attn_blocks(o4, q4, k4, v4, i4, n4), 10, 3)
+        d4 = nnz4 / (c4.B * c4.H * nb4 * nb4)
+        configs["c4_ragged"] = {"workload": c4.name, "density": d4, "full_attn_ms": ms_f,
+                                "full_attn_tflops": F4 / ms_f / 1e9, "full_attn_frac_of_peak": F4 / ms_f / 1e9 / peak,
+                                "block_lists_ms": ms_l, "block_lists_qk_tflops": F4 / 2 / ms_l / 1e9,
+                                "sparse_ms": ms_s, "sparse_tflops_on_kept_blocks": Fs4 / ms_s / 1e9,
+                                "sparse_frac_of_peak": Fs4 / ms_s / 1e9 / peak,
+                                "sparse_renorm_ms": ms_r, "sparse_renorm_tflops_on_kept_blocks": Fs4 / ms_r / 1e9,
+                                "sparse_speedup_over_full": ms_f / ms_s, "speedup_gap": (1.0 / d4) / (ms_f / ms_s),
+                                "union_overhead": union_overhead(i4, n4, nb4)}
+        capi.check()
+        del q4, k4, v4, o4, flush
+    barrier()
+
+    # ---- per rank record, max over ranks
+    mine = {"rank": rank, "gpu": gpu_index, "ms": ms_step, "ms_200": ms_200, "ms_burst20": ms_burst, "nnz": nnz,
+            "sm_mhz": clocks["sm_mhz"], "sm_mhz_200": clocks_200["sm_mhz"], "reasons": clocks["reasons"],
+            "reasons_200": clocks_200["reasons"]}
+    if e2e:
+        mine.update({"e2e_ms": e2e["full_ms"], "e2e_cached_lists_ms": e2e["cached_ms"], "copies_only_ms": e2e["copies_ms"],
+                     "h2d_gbs_in_copies_only": e2e["h2d"] / e2e["copies_ms"] / 1e6,
+                     "d2h_gbs_in_copies_only": e2e["d2h"] / e2e["copies_ms"] / 1e6})
+    per_rank = [mine]
     if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([ms_step, ms_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        f = torch.tensor([F_sparse], device=dev, dtype=torch.float64)
-        dist.all_reduce(f, op=dist.ReduceOp.SUM)
-        ms_all, ms_e2e_all, F_total = t[0].item(), t[1].item(), f[0].item()
-
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, mine)
     if rank == 0:
+        ms_all = max(r["ms"] for r in per_rank)
+        F_total = 4.0 * 64 * 64 * D * sum(r["nnz"] for r in per_rank)
         achieved = F_sparse / ms_step / 1e9                 # this rank's kernel, TFLOP/s
-        peak = peaks["bf16_tflops"]
+        slow = max(per_rank, key=lambda r: r["ms"])
         line = {
             "metric": METRIC, "value": F_total / ms_all / 1e9, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_all, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
-            "density": density, "kept_blocks_per_gpu": nnz,
-            "e2e": {"value": F_total / ms_e2e_all / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e_all,
-                    "api": "torch.ops.cuda_attn.sp_attn_blocks_ml on q, k, v copied from pinned host memory each step, "
-                           "o read back each step; steps double-buffered over copy-in / compute / copy-out streams"},
+            "density": density, "kept_blocks_per_gpu": nnz, "union_overhead": u_over,
+            "union_overhead_note": "64x64 block products issued per kept block: an item walks the union of two "
+                                   "neighbouring query blocks' lists on one 128-row tile, two key blocks per step",
+            "ms_per_step_burst": ms_burst, "ms_per_step_200": ms_200,
+            "clocks_burst": clocks_burst, "clocks_200": clocks_200,
+            "tflops_burst": F_sparse / ms_burst / 1e9, "tflops_200": F_sparse / ms_200 / 1e9,
             "gpu_launches": 2 * args.steps,          # per step: sparse_order_kernel + sparse_ml_persistent_kernel
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "sparse_ml_persistent_kernel<128>", "achieved": achieved,
+            "slowest_rank": {"rank": slow["rank"], "ms": slow["ms"], "nnz": slow["nnz"], "sm_mhz": slow["sm_mhz"],
+                             "reasons": slow["reasons"]},
+            "per_rank": per_rank,
+            "roofline": {"bound": "tensor", "kernel": f"sparse_ml_persistent_kernel<{D}>", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16_tflops (burst: kernel timed alone)",
-                         "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "traffic": None},
-            "stages": {
-                "full_attn_ms": ms_full, "full_attn_tflops": F_full / ms_full / 1e9,
-                "full_attn_frac_of_peak": F_full / ms_full / 1e9 / peak,
-                "block_lists_ms": ms_lists, "block_lists_qk_tflops": F_full / 2 / ms_lists / 1e9,
-                "maxq_denom_ms": ms_maxq, "maxq_denom_qk_tflops": F_full / 2 / ms_maxq / 1e9,
-                "mask_epilogue_note": "block_lists_ms - maxq_denom_ms (difference of two timings; the compaction "
-                                      "kernel alone is profiled in profiles/block_threshold_compact_c3_16heads.md)",
-                "mask_epilogue_ms": ms_lists - ms_maxq,
-                "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
-                "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
-                "booleanmask_128_ms": ms_tokmask, "booleanmask_128_listed_ms": ms_tokmask_listed,
-                "pack_mask_ms": ms_pack, "pack_mask_gbs": pack_bytes / ms_pack / 1e6,
-                "pack_mask_frac_of_hbm_peak": pack_bytes / ms_pack / 1e6 / peaks["hbm_gbs"],
-                "packedmask_to_indexmask_ms": ms_p2i, "packedmask_to_indexmask_gbs": pack_bytes / ms_p2i / 1e6,
-                "packedmask_to_indexmask_frac_of_hbm_peak": pack_bytes / ms_p2i / 1e6 / peaks["hbm_gbs"],
-                "booleanmask_to_indexmask_ms": ms_m2i, "booleanmask_to_indexmask_gbs": pack_bytes / 4.125 * 8 / ms_m2i / 1e6,
-                "topk_indices_ms": ms_topk, "topk_select_k": sel_k,
-                "sp_attn_threshold_tokens_ms": ms_tok_thr,
-                "sp_attn_threshold_tokens_tflops_on_listed_tokens": F_tok_thr / ms_tok_thr / 1e9,
-                "sp_attn_tokens_ms": ms_tok, "sp_attn_tokens_tflops_on_listed_tokens": F_tok / ms_tok / 1e9,
-                "sp_attn_blocks_renorm_ms": ms_renorm,
-                "sp_attn_blocks_renorm_tflops_on_kept_blocks": F_sparse / ms_renorm / 1e9,
-                "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
-                "sparse_ms": ms_step, "sparse_speedup_over_full": ms_full / ms_step,
-                "ideal_speedup_1_over_density": 1.0 / density,
-                "speedup_gap": (1.0 / density) / (ms_full / ms_step)},
+                         "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                         "frac_200_steps_of_sustained": F_sparse / ms_200 / 1e9 / peaks["bf16_tflops_sustained"],
+                         "traffic": NCU_DRAM_BYTES_PER_C3_HEAD * B * H if args.workload == "c3" else None,
+                         "traffic_source": "one ncu capture of a 16-head launch, scaled by heads"},
+            "stages": stages, "strong": strong, "configs": configs,
         }
-        # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
-        # profiles/sparse_ml_persistent_c3_16heads.md (16 heads: 312 MB), scaled by heads
-        if args.workload == "c3":
-            line["roofline"]["traffic"] = 312.0e6 * (w.B * w.H) / 16.0
+        if e2e:
+            e_full = max(r["e2e_ms"] for r in per_rank)
+            e_cached = max(r["e2e_cached_lists_ms"] for r in per_rank)
+            e_copy = max(r["copies_only_ms"] for r in per_rank)
+            line["e2e"] = {"value": F_total / e_full / 1e9, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"],
+                           "d2h_bytes_per_step": e2e["d2h"], "ms_per_step": e_full,
+                           "work_per_step": "threshold block lists + sparse attention (same work as the reference arm's step)",
+                           "api": "torch.ops.cuda_attn.block_index_lists + sp_attn_blocks_ml on q, k, v copied from "
+                                  "pinned host memory each step, o read back each step; steps double-buffered over "
+                                  "copy-in / compute / copy-out streams",
+                           "host_memory": e2e["host_kind"], "output_matches_resident_path": e2e["output_matches_resident_path"],
+                           "copies_only_ms_per_step": e_copy,
+                           "copies_only_note": "the same host<->device copies with no kernel: the host-side ceiling",
+                           "aggregate_h2d_gbs_copies_only": sum(r["h2d_gbs_in_copies_only"] for r in per_rank),
+                           "gpu_launches_per_step": 4}
+            line["e2e_cached_lists"] = {"value": F_total / e_cached / 1e9, "unit": UNIT, "ms_per_step": e_cached,
+                                        "api": "torch.ops.cuda_attn.sp_attn_blocks_ml alone on host q, k, v (lists built once)"}
         if world == 1 and not args.no_cpu_baseline:
             r = run_cpu(w, steps=2, warmup=1, budget_s=25.0)
             line["cpu_baseline"] = {k_: r[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}

@@ -26,6 +26,7 @@ PROTOTYPES = {
     "fgattn_status_string": (C.c_char_p, [_i]),
     "fgattn_last_cuda_error": (_i, []),
     "fgattn_check": (_i, [_vp, C.POINTER(_i)]),
+    "fgattn_set_tuning": (_i, [C.c_char_p, _i]),
     "fgattn_full_attn": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_fullattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_maxq_denom": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
@@ -43,6 +44,9 @@ PROTOTYPES = {
     "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
+    "fgattn_sp_attn_blocks_hint": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
+                                        _vp]),
+    "fgattn_selftest_bounded_wait": (_i, [_ll, _vp]),
     "fgattn_sp_attn_blocks": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "fgattn_topk_scratch_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "fgattn_topk_indices": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
@@ -109,7 +113,14 @@ def check(device=None) -> None:
     with torch.cuda.device(device):
         st = lib().fgattn_check(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(code))
     if st != OK:
-        raise FgattnError("fgattn_check", st, f"wait id {code.value}")
+        e = FgattnError("fgattn_check", st, f"wait id {code.value}")
+        e.code = code.value
+        raise e
+
+
+def set_tuning(name: str, value: int) -> None:
+    """Scheduling knobs ("group_heads", "dense_persist"); see fgattn_set_tuning in the header."""
+    _call("fgattn_set_tuning", name.encode(), int(value))
 
 
 def full_attn(o, q, k, v, kv_seq_len=None, scale=0.0):
@@ -208,6 +219,9 @@ def block_index_lists_noalloc(kb_indices, kb_counts, max_q, denom, q, k, thresho
                               scale=0.0):
     """fgattn_block_index_lists_noalloc: same results as block_index_lists, scratch built into the
     library (no allocation anywhere on this path; one (batch, head) unit must fit in 64 MiB)."""
+    # this entry point has no kv_rows argument: it reads k / v as [B, H, S, D]
+    if k.shape != q.shape or (v is not None and v.shape != q.shape) or (o is not None and o.shape != q.shape):
+        raise FgattnError("fgattn_block_index_lists_noalloc", 1, "k, v and o must have exactly the shape of q")
     _check_qkv(q, k, o, v)
     B, H, S, D = q.shape
     with torch.cuda.device(q.device):
@@ -230,6 +244,27 @@ def sp_attn_blocks_ml(o, q, k, v, kb_indices, kb_counts, max_q, denom, kv_seq_le
               kb_indices.shape[3], _ptr(max_q), _ptr(denom), B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale,
               _ptr(workspace),
               workspace.numel() * workspace.element_size(), _stream(q))
+
+
+def sp_attn_blocks_hint(o, q, k, v, kb_indices, kb_counts, max_q_hint, kv_seq_len=None, scale=0.0, workspace=None):
+    """Renormalising block-sparse attention on the persistent kernel; max_q_hint [B,H,1,S_pad] is a
+    per-row estimate of the row maximum (e.g. the max_q of the pass that built the lists)."""
+    _check_qkv(o, q, k, v)
+    B, H, S, D = q.shape
+    if workspace is None:
+        workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _call("fgattn_sp_attn_blocks_hint", _ptr(o), _ptr(q), _ptr(k), _ptr(v), _ptr(kb_indices), _ptr(kb_counts),
+              kb_indices.shape[3], _ptr(max_q_hint), B, H, S, D, k.shape[2], kv_seq_len or k.shape[2], scale,
+              _ptr(workspace), workspace.numel() * workspace.element_size(), _stream(q))
+    return workspace
+
+
+def selftest_bounded_wait(budget_cycles: int = 100000, device=None) -> None:
+    """Launch the one-warp probe whose bounded wait is left to run out; the next check() raises
+    FgattnError(DEVICE_TIMEOUT) with wait id 9001."""
+    with torch.cuda.device(device):
+        _call("fgattn_selftest_bounded_wait", int(budget_cycles), C.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
 def sp_attn_blocks(o, q, k, v, kb_indices, kb_counts, kv_seq_len=None, scale=0.0, workspace=None, ordered=True):

@@ -2,24 +2,38 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/fgattn_b200.h"
 #include "dense_attn.cuh"
 #include "mask_kernels.cuh"
 #include "packed_mask.cuh"
+#include "selftest.cuh"
 #include "sparse_attn.cuh"
 #include "sparse_ml_persistent.cuh"
 #include "sparse_token_attn.cuh"
 #include "tensor_map.h"
 #include "topk_select.cuh"
 
+// Scratch and error word of the allocation-free entry point live in the library image.  In host code
+// the names below are host-side stand-ins, not device addresses: the device addresses are looked up
+// once per device with cudaGetSymbolAddress and only those are handed to kernels.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[FGATTN_NOALLOC_SCRATCH_BYTES];
+static __device__ __align__(256) int g_noalloc_err_word;
+
 namespace {
 
 thread_local int g_last_cuda_error = 0;
 std::mutex g_mutex;
 int* g_err_word[64] = {nullptr};
+struct NoAllocAddrs {
+  void* scratch = nullptr;
+  int* err = nullptr;
+};
+NoAllocAddrs g_noalloc_addrs[64];
 
 int cuda_fail(cudaError_t e) {
   g_last_cuda_error = int(e);
@@ -48,6 +62,25 @@ int get_err_word(int** out) {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Tuning overrides from the environment, read once per process: FGATTN_GROUP_HEADS (units per group of
+// the longest-first thread-block orders; 0 = the built-in choice), FGATTN_DENSE_PERSIST (1 / 0 forces
+// the persistent / one-item form of the dense family; -1 = by key length).
+// fgattn_set_tuning overrides either for the rest of the process.
+constexpr int kTuningUnset = -2147483647 - 1;
+std::atomic<int> g_tune_group_heads{kTuningUnset}, g_tune_dense_persist{kTuningUnset};
+int env_group_heads() {
+  const int t = g_tune_group_heads.load(std::memory_order_relaxed);
+  if (t != kTuningUnset) return t;
+  static const int v = [] { const char* e = getenv("FGATTN_GROUP_HEADS"); return e ? atoi(e) : 0; }();
+  return v;
+}
+int env_dense_persist() {
+  const int t = g_tune_dense_persist.load(std::memory_order_relaxed);
+  if (t != kTuningUnset) return t;
+  static const int v = [] { const char* e = getenv("FGATTN_DENSE_PERSIST"); return e ? atoi(e) : -1; }();
+  return v;
+}
 
 // S = query rows, kv_rows = rows of the k / v tensors per head, kv_len = leading k / v rows that take part
 int check_qk(const void* q, const void* k, int B, int H, int S, int D, int kv_rows, int kv_len) {
@@ -109,7 +142,7 @@ int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
   pp.n_pairs = (p.S + 255) / 256;
   pp.n_items = pp.n_pairs * nbh;
   if constexpr (MODE != fg::kTokenMask && !BLOCKMAX) {
-    static const int persist_env = getenv("FGATTN_DENSE_PERSIST") ? atoi(getenv("FGATTN_DENSE_PERSIST")) : -1;
+    const int persist_env = env_dense_persist();
     const bool persist = persist_env >= 0 ? persist_env != 0 : p.n_kv_tiles <= kPersistMaxKeyTiles;
     if (persist) {
       int sms = 0;
@@ -152,9 +185,10 @@ int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int 
 }
 
 // Renormalising block-sparse attention (two-slot kernel).
+// `redo` (optional, [B*H * ceil(S/128)] flags): re-run pass, only the marked pairs of query blocks are computed.
 int launch_sparse(void* o, const void* q, const void* k, const void* v, const int* kb_idx, const int* kb_cnt,
                   int list_stride, int B, int H, int S, int D, int kv_rows, int kv_len, float scale, void* workspace,
-                  size_t workspace_bytes, cudaStream_t st) {
+                  size_t workspace_bytes, cudaStream_t st, const int* redo = nullptr) {
   int r = check_qk(q, k, B, H, S, D, kv_rows, kv_len);
   if (r) return r;
   if (!o || !v || !kb_idx || !kb_cnt) return FGATTN_INVALID_ARGUMENT;
@@ -182,13 +216,15 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
       fg::make_qkv_map(&mv, v, B * H, kv_rows, D, 64))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   p.quads = (S + 255) / 256;
+  p.redo = redo;
+  p.npairs = (S + 127) / 128;
   const int n_units = B * H;
   if ((long long)n_units * p.quads > 2147483647LL) return FGATTN_UNSUPPORTED;
   if (workspace) {
     // CTA order: units in groups whose K/V (<= 64 MiB) stays in L2, inside a group longest lists first
     const size_t kv_bytes_per_unit = size_t(4) * kv_rows * D;
     int group = int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit));
-    if (const char* gh = getenv("FGATTN_GROUP_HEADS")) group = atoi(gh);   // tuning override
+    if (env_group_heads() > 0) group = env_group_heads();                // tuning override
     group = std::max(1, std::min(group, n_units));
     const int n_groups = (n_units + group - 1) / group;
     group = (n_units + n_groups - 1) / n_groups;                      // groups of equal size
@@ -238,20 +274,41 @@ const char* fgattn_status_string(int status) {
 
 int fgattn_last_cuda_error(void) { return g_last_cuda_error; }
 
+int fgattn_set_tuning(const char* name, int value) {
+  if (!name) return FGATTN_INVALID_ARGUMENT;
+  if (!strcmp(name, "group_heads")) g_tune_group_heads.store(value < 0 ? kTuningUnset : value);
+  else if (!strcmp(name, "dense_persist")) g_tune_dense_persist.store(value < -1 ? kTuningUnset : value);
+  else return FGATTN_INVALID_ARGUMENT;
+  return FGATTN_OK;
+}
+
 int fgattn_check(void* stream, int* code) {
-  int* w = nullptr;
-  int r = get_err_word(&w);
-  if (r) return r;
+  // Two words can hold a time-out: the allocated one that most entry points use, and the one built into
+  // the library that the allocation-free entry point uses while the first does not exist.  Only words that
+  // some call has put to use are read, so this function itself never allocates.
+  int dev = 0;
+  FG_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FGATTN_UNSUPPORTED;
+  int* words[2];
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    words[0] = g_err_word[dev];
+    words[1] = g_noalloc_addrs[dev].err;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   FG_CUDA(cudaStreamSynchronize(st));
-  int h = 0;
-  FG_CUDA(cudaMemcpy(&h, w, sizeof(int), cudaMemcpyDeviceToHost));
-  if (code) *code = h;
-  if (h != 0) {
-    FG_CUDA(cudaMemset(w, 0, sizeof(int)));
-    return FGATTN_DEVICE_TIMEOUT;
+  int first = 0;
+  for (int* w : words) {
+    if (!w) continue;
+    int h = 0;
+    FG_CUDA(cudaMemcpy(&h, w, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h != 0) {
+      FG_CUDA(cudaMemset(w, 0, sizeof(int)));
+      if (first == 0) first = h;
+    }
   }
-  return FGATTN_OK;
+  if (code) *code = first;
+  return first != 0 ? FGATTN_DEVICE_TIMEOUT : FGATTN_OK;
 }
 
 int fgattn_full_attn(void* o, const void* q, const void* k, const void* v, int batch, int heads, int seq, int D,
@@ -325,7 +382,7 @@ int token_mask_launch(int* booleanmask, float threshold, int mask_stride, const 
     const int n_units = batch * heads, quads = (seq + 255) / 256;
     const size_t k_bytes_per_unit = size_t(4) * kv_rows * D;
     int group = int(std::max<size_t>(1, (size_t(256) << 20) / k_bytes_per_unit));
-    if (const char* gh = getenv("FGATTN_GROUP_HEADS")) group = atoi(gh);   // tuning override
+    if (env_group_heads() > 0) group = env_group_heads();                // tuning override
     group = std::max(1, std::min(group, n_units));
     const int n_groups = (n_units + group - 1) / group;
     group = (n_units + n_groups - 1) / n_groups;
@@ -418,7 +475,7 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
     // storage order, 0.77 ms with 4 heads per group, 0.55 ms with all 12), so groups span up to 256 MiB of K/V.
     const size_t kv_bytes_per_unit = size_t(4) * kv_rows * D;
     int group = int(std::max<size_t>(1, (size_t(256) << 20) / kv_bytes_per_unit));
-    if (const char* gh = getenv("FGATTN_GROUP_HEADS")) group = atoi(gh);   // tuning override
+    if (env_group_heads() > 0) group = env_group_heads();                // tuning override
     group = std::max(1, std::min(group, n_units));
     const int n_groups = (n_units + group - 1) / group;
     group = (n_units + n_groups - 1) / n_groups;                      // groups of equal size
@@ -490,19 +547,7 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
 }
 
 // ---- allocation-free variant of fgattn_block_index_lists --------------------------------------
-// Scratch and error word live in the library image.  In host code the names below are host-side
-// stand-ins, not device addresses: the device addresses are looked up once per device with
-// cudaGetSymbolAddress and only those are handed to kernels.
-static __device__ __align__(256) unsigned char g_noalloc_scratch[FGATTN_NOALLOC_SCRATCH_BYTES];
-static __device__ __align__(256) int g_noalloc_err_word;
-
 namespace {
-struct NoAllocAddrs {
-  void* scratch = nullptr;
-  int* err = nullptr;
-};
-NoAllocAddrs g_noalloc_addrs[64];
-
 // First use on a device: resolve the device addresses of the built-in arrays (no allocation).
 int noalloc_addrs(NoAllocAddrs* out) {
   int dev = 0;
@@ -579,17 +624,22 @@ int fgattn_block_index_lists_noalloc(int* kb_indices, int* kb_counts, int list_s
 
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq) {
   if (batch <= 0 || heads <= 0 || seq <= 0) return 0;
+  // [0, 4): queue counter (+ padding); then the processing order of the items; then their re-run flags
   const size_t npairs = size_t((seq + 127) / 128);
-  return 16 + size_t(batch) * heads * npairs * sizeof(int);
+  return 16 + 2 * size_t(batch) * heads * npairs * sizeof(int);
 }
 
-int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+namespace {
+// The persistent block-sparse kernel in its two forms: probabilities from the given (max_q, denom), or
+// (renorm) renormalised over the kept keys with max_q as the fixed per-row exponent offset, followed by
+// the re-run pass over the items that left the safe exponent range.
+int launch_sparse_persistent(bool renorm, void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                              const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
                              int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream) {
   int r = check_qk(q, k, batch, heads, seq, D, kv_rows, kv_seq_len);
   if (r) return r;
-  if (!o || !v || !kb_indices || !kb_counts || !max_q || !denom || !workspace || list_stride < 1)
+  if (!o || !v || !kb_indices || !kb_counts || !max_q || (!renorm && !denom) || !workspace || list_stride < 1)
     return FGATTN_INVALID_ARGUMENT;
   if (!aligned16(o) || !aligned16(v) || !aligned16(workspace)) return FGATTN_MISALIGNED;
   if (workspace_bytes < fgattn_sp_attn_workspace_bytes(batch, heads, seq)) return FGATTN_SCRATCH_TOO_SMALL;
@@ -601,8 +651,6 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
   p.denom = denom;
   p.kb_idx = kb_indices;
   p.kb_cnt = kb_counts;
-  p.queue = static_cast<int*>(workspace);
-  p.order = static_cast<int*>(workspace) + 4;
   p.S = seq;
   p.S_pad = ((seq + 127) / 128) * 128;
   p.kv_len = kv_seq_len;
@@ -610,48 +658,85 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
   p.nkb = (kv_seq_len + 63) / 64;
   p.npairs = (seq + 127) / 128;
   p.n_items = batch * heads * p.npairs;
+  p.queue = static_cast<int*>(workspace);
+  p.order = static_cast<int*>(workspace) + 4;
+  p.redo = static_cast<int*>(workspace) + 4 + p.n_items;
   p.list_stride = list_stride;
   p.list_cap = p.nkb + 2;
   p.scale_log2 = resolve_scale_log2(scale, D);
+#ifdef FG_STATS
   if (const char* dbg = getenv("FGATTN_DEBUG_SPARSE")) p.debug = atoi(dbg);
   if ((p.debug & 8) && workspace_bytes >= fgattn_sp_attn_workspace_bytes(batch, heads, seq) + 256 * 32 * 8 + 64)
     p.stats = reinterpret_cast<long long*>(static_cast<char*>(workspace) +
                                            ((fgattn_sp_attn_workspace_bytes(batch, heads, seq) + 63) / 64) * 64);
+#endif
   r = get_err_word(&p.err);
   if (r) return r;
   CUtensorMap mq, mk, mv;
   if (fg::make_qkv_map(&mq, q, batch * heads, seq, D, 128) || fg::make_qkv_map(&mk, k, batch * heads, kv_rows, D, 64) ||
       fg::make_qkv_map(&mv, v, batch * heads, kv_rows, D, 64))
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
-  int dev = 0, sms = 0;
-  FG_CUDA(cudaGetDevice(&dev));
-  FG_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0;
+  r = sm_count(&sms);
+  if (r) return r;
   // heads per queue group: enough items to balance the SMs (about six per SM), K/V of a group <= 64 MiB
   const int n_units = batch * heads;
   const size_t kv_bytes_per_unit = size_t(4) * kv_rows * D;
   int group_heads = (6 * sms + p.npairs - 1) / p.npairs;
   group_heads = std::min<int>(group_heads, int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit)));
-  if (const char* gh = getenv("FGATTN_GROUP_HEADS")) group_heads = atoi(gh);   // tuning override
+  if (env_group_heads() > 0) group_heads = env_group_heads();            // tuning override
   group_heads = std::max(1, std::min(group_heads, n_units));
   fg::sparse_order_kernel<<<(n_units + group_heads - 1) / group_heads, 256, 0, st>>>(
-      kb_counts, static_cast<int*>(workspace) + 4, p.queue, p.nqb, p.npairs, n_units, group_heads);
+      kb_counts, static_cast<int*>(workspace) + 4, p.queue, p.nqb, p.npairs, n_units, group_heads, 1, 2, 0,
+      renorm ? p.redo : nullptr);
   FG_CUDA(cudaGetLastError());
   const int grid = std::min(p.n_items, sms);
-  if (D == 128) {
-    const int smem = fg::SparseMLCfg<128>::smem_bytes(p.list_cap, p.nkb);
-    if (smem > 232448) return FGATTN_UNSUPPORTED;
-    auto kern = fg::sparse_ml_persistent_kernel<128>;
-    r = set_smem(kern, smem);
-    if (r) return r;
-    kern<<<grid, fg::SparseMLCfg<128>::kThreads, smem, st>>>(mq, mk, mv, p);
-  } else {
-    const int smem = fg::SparseMLCfg<64>::smem_bytes(p.list_cap, p.nkb);
-    if (smem > 232448) return FGATTN_UNSUPPORTED;
-    auto kern = fg::sparse_ml_persistent_kernel<64>;
-    r = set_smem(kern, smem);
-    if (r) return r;
-    kern<<<grid, fg::SparseMLCfg<64>::kThreads, smem, st>>>(mq, mk, mv, p);
-  }
+  const int smem = (D == 128) ? fg::SparseMLCfg<128>::smem_bytes(p.list_cap, p.nkb)
+                              : fg::SparseMLCfg<64>::smem_bytes(p.list_cap, p.nkb);
+  if (smem > 232448) return FGATTN_UNSUPPORTED;
+  auto go = [&](auto kern, int threads) -> int {
+    int rr = set_smem(kern, smem);
+    if (rr) return rr;
+    kern<<<grid, threads, smem, st>>>(mq, mk, mv, p);
+    return FGATTN_OK;
+  };
+  if (D == 128)
+    r = renorm ? go(fg::sparse_ml_persistent_kernel<128, true>, fg::SparseMLCfg<128>::kThreads)
+               : go(fg::sparse_ml_persistent_kernel<128, false>, fg::SparseMLCfg<128>::kThreads);
+  else
+    r = renorm ? go(fg::sparse_ml_persistent_kernel<64, true>, fg::SparseMLCfg<64>::kThreads)
+               : go(fg::sparse_ml_persistent_kernel<64, false>, fg::SparseMLCfg<64>::kThreads);
+  if (r) return r;
+  FG_CUDA(cudaGetLastError());
+  if (renorm)   // items whose rows left the safe exponent range run again with the running maximum
+    return launch_sparse(o, q, k, v, kb_indices, kb_counts, list_stride, batch, heads, seq, D, kv_rows, kv_seq_len,
+                         scale, nullptr, 0, st, p.redo);
+  return FGATTN_OK;
+}
+}  // namespace
+
+int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                             const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
+                             int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  return launch_sparse_persistent(false, o, q, k, v, kb_indices, kb_counts, list_stride, max_q, denom, batch, heads, seq,
+                                  D, kv_rows, kv_seq_len, scale, workspace, workspace_bytes, stream);
+}
+
+int fgattn_sp_attn_blocks_hint(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                               const int* kb_counts, int list_stride, const float* max_q_hint, int batch, int heads,
+                               int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  return launch_sparse_persistent(true, o, q, k, v, kb_indices, kb_counts, list_stride, max_q_hint, nullptr, batch,
+                                  heads, seq, D, kv_rows, kv_seq_len, scale, workspace, workspace_bytes, stream);
+}
+
+int fgattn_selftest_bounded_wait(long long budget_cycles, void* stream) {
+  if (budget_cycles < 1 || budget_cycles > 100000000LL) return FGATTN_INVALID_ARGUMENT;
+  int* err = nullptr;
+  int r = get_err_word(&err);
+  if (r) return r;
+  fg::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(err, budget_cycles);
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;
 }

@@ -77,8 +77,10 @@ struct AbortState {
 constexpr long long kWaitBudgetCycles = 3000000000LL;   // roughly 1.5-2 s at B200 clocks
 
 // Bounded wait.  Returns false when the CTA is aborting (own time-out or somebody else's).
-// `code` identifies the barrier in the error word written to `err` (global, may be null).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
+// `code` identifies the barrier in the error word written to `err` (global, may be null);
+// `budget` is the number of cycles after which the waiter gives up.
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code,
+                                                 long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
@@ -86,13 +88,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, AbortSt
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (ab->flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget) {
         ab->flag = 1;
         if (err) atomicCAS(err, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
+  return mbar_wait_budget(bar, parity, ab, err, code, kWaitBudgetCycles);
 }
 
 // Same bounded wait for roles whose waits are long and not latency critical (TMA producers, the

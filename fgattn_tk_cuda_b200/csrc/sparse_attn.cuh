@@ -27,6 +27,11 @@ struct SparseParams {
   // 64-row query blocks.  An order with the long lists first keeps the end of the launch short.
   const int* order;
   int quads;
+  // Re-run pass behind the fixed-offset persistent kernel: redo[unit * npairs + pair] != 0 marks a pair of
+  // query blocks (128 rows) whose rows left the safe exponent range there; a CTA whose two pairs are both
+  // unmarked returns at once.  Null = every item is computed.
+  const int* redo;
+  int npairs;
   float scale_log2;
 };
 
@@ -79,6 +84,11 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
   const int bh = item / p.quads;
   const int q0 = (item - bh * p.quads) * 256;
   const int words = (p.nkb + 31) / 32;
+  if (p.redo) {
+    const int pr = (item - bh * p.quads) * 2;
+    const int* f = p.redo + size_t(bh) * p.npairs + pr;
+    if (f[0] == 0 && (pr + 1 >= p.npairs || f[1] == 0)) return;       // CTA-uniform: nothing to re-run here
+  }
 
   if (tid == 0) {
     ab->flag = 0;

@@ -24,6 +24,18 @@
 // (buffer, pair), i.e. per step mod 6, because a parity wait must see every phase of its barrier.
 // Service warps after the softmax warps: TMA producer of Q and the K ring, Q K^T issuer, scheduler
 // (queue + union lists, up to three items ahead), P V issuer, TMA producer of the V ring.
+//
+// RENORM = true is the renormalising form (softmax over the kept keys only, what the sp_attn operator
+// computes) on the same schedule.  A softmax is invariant under a shift of its exponents, and the
+// running maximum of the online form is only there to keep the exponentials in range, so each row
+// uses a FIXED offset instead: p = 2^(s*c - hint*c) with `hint` a per-row estimate of the row maximum
+// handed in by the caller (the max_q of the pass that built the lists is a good one even when q has
+// moved on by a diffusion step: anything within about +-60 of the true maximum in the log2 domain
+// works, because bf16 probabilities and the fp32 accumulator keep their relative precision over that
+// range).  Every softmax thread sums the probabilities it produced, the four warpgroups' partial sums
+// of a row meet in shared memory once per item, and the epilogue scales the accumulator by 1/l.  A row
+// whose sum left the safe range (overflow: inf / NaN, underflow: below 2^-60) marks its item in
+// `redo`; the host then re-runs the marked items on the kernel with the running maximum.
 #pragma once
 #include "sm100_ptx.cuh"
 #include "softmax_steps.cuh"
@@ -41,10 +53,11 @@ struct SparseMLParams {
   const int* order;          // [BH * npairs] item ids (unit * npairs + pair) in queue order
   int* queue;                // global item counter (zeroed before the launch)
   int* err;
+  int* redo;                 // RENORM: [BH * npairs] flags (zeroed before the launch); 1 = item must be re-run
   int S, S_pad, kv_len, nqb, nkb, npairs, n_items, list_stride, list_cap;
   float scale_log2;
-  long long* stats;          // debug & 8: per-CTA cycle counters [gridDim.x][32]
-  int debug;                 // timing experiments only: 1 = no K/V loads, 2 = no UMMA, 4 = no softmax math
+  long long* stats;          // tuning builds (-DFG_STATS), debug & 8: per-CTA cycle counters [gridDim.x][32]
+  int debug;                 // tuning builds only: 1 = no K/V loads, 2 = no UMMA, 4 = no softmax math
 };
 
 template <int D>
@@ -68,9 +81,11 @@ struct SparseMLCfg {
   static constexpr int kOffV = kOffK + kKStages * kTileBytes;
   static constexpr int kOffBar = kOffV + kVStages * kTileBytes;
   static constexpr int kBarBytes = 768;
-  static constexpr int kOffList = kOffBar + kBarBytes;   // [kListBufs][list_cap] entries, then [2][words] bitmaps
+  // [kListBufs][list_cap] entries, then [2][words] bitmaps, then [4][4][128] partial row sums (RENORM)
+  static constexpr int kOffList = kOffBar + kBarBytes;
+  static constexpr int kRowSumBytes = 4 * kSmWGs * 128 * 4;
   static __host__ __device__ constexpr int smem_bytes(int list_cap, int nkb) {
-    return kOffList + kListBufs * list_cap * 4 + 2 * ((nkb + 31) / 32) * 4 + 1024;
+    return kOffList + kListBufs * list_cap * 4 + 2 * ((nkb + 31) / 32) * 4 + kRowSumBytes + 1024;
   }
 };
 
@@ -89,20 +104,22 @@ enum : int {
   PB_O_FULL = 37,
   PB_O_EMPTY = 38,
   PB_P_FULL = 40,      // +(step % 6) * 2 + key block of the step (12)
-  PB_COUNT = 52
+  PB_L_FULL = 52,      // +(item % 4) (4): RENORM, the item's partial row sums are in shared memory
+  PB_COUNT = 56
 };
 
 struct ItemInfo {
   int n_steps;   // -1: queue exhausted
   int bh;
   int pair;
-  int pad;
+  int halves;    // bit h: the 64-row query block h of the pair has a non-empty list
 };
 
-// N score columns -> N/2 packed bf16 probability columns, p = 2^(s*c - t_row).
-template <int N>
+// N score columns -> N/2 packed bf16 probability columns, p = 2^(s*c - t_row).  SUM: the
+// probabilities are also added to the two running sums.
+template <int N, bool SUM>
 __device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[N / 2], int valid, float c,
-                                         float t_row) {
+                                         float t_row, float& sum0, float& sum1) {
   const uint64_t c2 = f2_pack(c, c), nt2 = f2_pack(-t_row, -t_row);
 #pragma unroll
   for (int i = 0; i < N; i += 2) {
@@ -112,6 +129,10 @@ __device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[
     if (valid < N) {
       if (i >= valid) p0 = 0.f;
       if (i + 1 >= valid) p1 = 0.f;
+    }
+    if (SUM) {
+      sum0 += p0;
+      sum1 += p1;
     }
     pk[i >> 1] = pack_bf16(p0, p1);
   }
@@ -126,7 +147,7 @@ __device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[
 #define FG_CLK() 0ll
 #endif
 
-template <int D>
+template <int D, bool RENORM>
 __global__ void __launch_bounds__(SparseMLCfg<D>::kThreads, 1)
 sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                             const __grid_constant__ CUtensorMap mv, const SparseMLParams p) {
@@ -145,6 +166,12 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int words = (p.nkb + 31) / 32;
+  float* rowsum = reinterpret_cast<float*>(bitmaps + 2 * words);                                             // [4][4][128]
+#ifdef FG_STATS
+  const int dbg = p.debug;
+#else
+  constexpr int dbg = 0;               // the timing experiments exist in tuning builds only
+#endif
   constexpr uint32_t kColS = 0, kColO = 384;           // three 128-column score buffers, then the accumulator
   constexpr int kSB = 3;
 
@@ -171,6 +198,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     }
     mbar_init(bar(PB_O_FULL), 1);
     mbar_init(bar(PB_O_EMPTY), Cfg::kSmWarps);
+    for (int i = 0; i < 4; ++i) mbar_init(bar(PB_L_FULL + i), Cfg::kSmWarps);
     mbar_fence_init();
   }
   if (warp == Cfg::kWarpProdK) {
@@ -264,6 +292,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         }
         info[lb].bh = bh;
         info[lb].pair = pair;
+        info[lb].halves = (n_half[0] > 0 ? 1 : 0) | (n_half[1] > 0 ? 2 : 0);
         info[lb].n_steps = base >> 1;
         mbar_arrive(bar(PB_LIST_FULL + lb));
       }
@@ -313,7 +342,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
             if (f > 0) ok = mbar_wait_relaxed(bar(empty0 + st), (f - 1) & 1, ab, p.err, 1104);
             if (!ok) break;
             const uint32_t dst = ring + st * Cfg::kTileBytes, full_bar = bar(full0 + st);
-            if (p.debug & 1) {
+            if (dbg & 1) {
               mbar_arrive(full_bar);
             } else {
               mbar_arrive_expect_tx(full_bar, Cfg::kTileBytes);
@@ -360,7 +389,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           if (!ok) break;
           tc_fence_after();
           const uint32_t ka = sbase + Cfg::kOffK + ks * Cfg::kTileBytes;
-          if (!(p.debug & 2)) {
+          if (!(dbg & 2)) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
               const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
@@ -406,7 +435,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
             FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + (s % 6) * 2 + kb), (s / 6) & 1, ab, p.err, 1304));
             if (!ok) break;
             tc_fence_after();
-            if (!(p.debug & 2)) {
+            if (!(dbg & 2)) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) {
                 const int ks = kb * 4 + kk;                   // 16-key step inside the 128-key tile
@@ -448,9 +477,22 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     int pe_par = 0;
     __nv_bfloat16* pe_orow = nullptr;
     bool pe_in = false;
+    int pe_u = 0, pe_item = 0;                           // RENORM: item counter / global item id of the pending rows
+    bool pe_listed = false;                              // RENORM: this row's query block has a non-empty list
     auto epilogue = [&]() {
       FG_TW(w_epi, ok = mbar_wait(bar(PB_O_FULL), pe_par, ab, p.err, 1401));
       if (!ok) return;
+      float inv = 1.0f;
+      if constexpr (RENORM) {
+        // the four warpgroups' partial sums of this row; the row's output is O / l
+        FG_TW(w_epi, ok = mbar_wait(bar(PB_L_FULL + (pe_u & 3)), (pe_u >> 2) & 1, ab, p.err, 1404));
+        if (!ok) return;
+        const float* ls = rowsum + (pe_u & 3) * (Cfg::kSmWGs * 128) + row_in_tile;
+        const float l = (ls[0] + ls[128]) + (ls[256] + ls[384]);
+        const bool good = (l >= 0x1p-60f) && (l <= 0x1p100f);        // false for NaN, too
+        inv = good ? 1.0f / l : 0.f;
+        if (pe_in && pe_listed && !good) p.redo[pe_item] = 1;
+      }
       long long te0 = FG_CLK();
       tc_fence_after();
       uint32_t o[kOCols];
@@ -469,6 +511,10 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 #pragma unroll
         for (int i = 0; i < kOCols / 8; ++i) {
           uint4 v;
+          if constexpr (RENORM) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[8 * i + e] = __float_as_uint(__uint_as_float(o[8 * i + e]) * inv);
+          }
           v.x = pack_bf16(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
           v.y = pack_bf16(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
           v.z = pack_bf16(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
@@ -485,7 +531,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       if (!ok) break;
       const int n = info[lb].n_steps;
       if (n < 0) break;
-      const int bh = info[lb].bh, pair = info[lb].pair;
+      const int bh = info[lb].bh, pair = info[lb].pair, halves = info[lb].halves;
       const int row = pair * 128 + row_in_tile;
       __nv_bfloat16* orow = p.o + (size_t(bh) * p.S + row) * D;
       if (n == 0) {
@@ -498,8 +544,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         long long tp0 = FG_CLK();
         if (row < p.S) {
           const size_t off = size_t(bh) * p.S_pad + row;
-          t_row = p.max_q[off] * c + log2f(p.denom[off]);
+          t_row = RENORM ? p.max_q[off] * c : p.max_q[off] * c + log2f(p.denom[off]);
         }
+        float sum0 = 0.f, sum1 = 0.f;                    // RENORM: this thread's share of the row sum
 #ifdef FG_STATS
         if (t_row == 12345.678f) t_prol += 1;            // keeps the loads inside the timed span
 #endif
@@ -529,11 +576,11 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           for (int ch = 0; ch < 2; ++ch) {
             const int valid = max(0, min(32, valid_kb - ch * 32));
             uint32_t pk[16];
-            if (valid > 0 && !(p.debug & 4)) {           // warp-uniform
+            if (valid > 0 && !(dbg & 4)) {               // warp-uniform
               uint32_t r[32];
               tmem_ld32(a + ch * 32, r);
               tmem_ld_wait();
-              ml_probs<32>(r, pk, valid, c, t_row);
+              ml_probs<32, RENORM>(r, pk, valid, c, t_row, sum0, sum1);
             } else {
 #pragma unroll
               for (int i = 0; i < 16; ++i) pk[i] = 0u;
@@ -555,6 +602,16 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         if (!ok) break;
         if (pe) epilogue();                              // (only when the loop above did not run it)
         if (!ok) break;
+        if constexpr (RENORM) {
+          // A buffer of four items: a warpgroup can be at most three steps (so three items) ahead of the
+          // P*V issuer, which starts the item after next only once every warp has read this one's sums.
+          rowsum[(u & 3) * (Cfg::kSmWGs * 128) + wg * 128 + row_in_tile] = sum0 + sum1;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(PB_L_FULL + (u & 3)));
+          pe_u = u;
+          pe_item = bh * p.npairs + pair;
+          pe_listed = (halves >> half) & 1;
+        }
         pe = true;
         pe_par = u & 1;
         pe_orow = orow;
@@ -590,10 +647,12 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 // union of `elems` consecutive lists (their lengths are added): the persistent block kernel has
 // subs 1 / elems 2, the two-slot block kernel 2 / 2, the token-list kernel 2 / 1.  Lengths are
 // bucketed as (length >> shift).  Counting sort; ties land in arbitrary order, which only affects
-// scheduling.  grid (number of groups), 256 threads.  Block 0 also clears the queue counter.
+// scheduling.  grid (number of groups), 256 threads.  Block 0 also clears the queue counter; with `redo`
+// every block clears the re-run flags of its items.
 __global__ void __launch_bounds__(256)
 sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int* __restrict__ queue, int nqb,
-                    int npairs, int n_units, int group_heads, int subs = 1, int elems = 2, int shift = 0) {
+                    int npairs, int n_units, int group_heads, int subs = 1, int elems = 2, int shift = 0,
+                    int* __restrict__ redo = nullptr) {
   constexpr int kBuckets = 1024;
   __shared__ int hist[kBuckets];
   __shared__ int part[256];
@@ -601,6 +660,8 @@ sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int
   const int u0 = blockIdx.x * group_heads, u1 = min(n_units, u0 + group_heads);
   const int n = (u1 - u0) * npairs;
   if (blockIdx.x == 0 && tid == 0) *queue = 0;
+  if (redo)
+    for (int i = tid; i < n; i += 256) redo[size_t(u0) * npairs + i] = 0;
   for (int i = tid; i < kBuckets; i += 256) hist[i] = 0;
   __syncthreads();
   auto length_of = [&](int i) {

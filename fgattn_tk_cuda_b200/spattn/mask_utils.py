@@ -79,15 +79,19 @@ class CompressedBitMaskCache(BitMaskCache):
 class CompressedListCache(NaiveMaskCache):
     """Caches index lists (key tokens or 64-key blocks) as one bit per entry: 1/32 of the int32 lists.
     `width` = number of list targets (keys or key blocks); lists come back ascending, unused slots
-    filled with the list stride."""
+    filled with the list stride.  Tensors handed over after the counts (the max_q hint of the block mode)
+    are kept as they are and come back behind the lists."""
 
     def get_mask_from_cache(self, layer):
-        packed, width, stride = self.cache[layer]
-        return packedmask_to_indexmask_cuda(packed, width, stride=stride)
+        packed, width, stride, extra = self.cache[layer]
+        return (*packedmask_to_indexmask_cuda(packed, width, stride=stride), *extra)
 
-    def update_cache(self, layer, indices, num_indices, width=None):
+    def update_cache(self, layer, indices, num_indices, *extra, width=None):
+        if extra and isinstance(extra[0], int):
+            width, extra = extra[0], extra[1:]
         width = indices.shape[-1] if width is None else width
-        self.cache[layer] = (indexmask_to_packedmask_cuda(indices, num_indices, width), width, indices.shape[-1])
+        self.cache[layer] = (indexmask_to_packedmask_cuda(indices, num_indices, width), width, indices.shape[-1],
+                             tuple(extra))
 
 
 def pack(mask: torch.Tensor) -> torch.Tensor:
@@ -211,16 +215,30 @@ _scratch = {}
 
 
 def _block_scratch(q, k=None):
+    """Block-maxima scratch of the one-pass list builder, cached per (device, current stream): calls on
+    one stream are serialised by it and share the buffer, calls on different streams (or host threads
+    working on different streams) get their own.  release_block_scratch() drops the buffers."""
     B, H, S, _ = q.shape
     need = cuda_attn.block_scratch_bytes(B, H, S, S if k is None else k.shape[2])
     per_head = need // (B * H)
+    key = (q.device, torch.cuda.current_stream(q.device).cuda_stream)
+    have = _scratch.get(key)
+    if have is not None and have.numel() * 4 >= need:
+        return have
     free, _total = torch.cuda.mem_get_info(q.device)
     heads_fit = max(1, min(B * H, int(free * 0.5) // per_head))     # fewer heads -> the op loops over chunks
     want = per_head * heads_fit
-    have = _scratch.get(q.device)
     if have is None or have.numel() * 4 < want:
-        _scratch[q.device] = have = torch.empty(want // 4, dtype=torch.float32, device=q.device)
+        _scratch.pop(key, None)
+        have = None
+        _scratch[key] = have = torch.empty(want // 4, dtype=torch.float32, device=q.device)
     return have
+
+
+def release_block_scratch():
+    """Free the cached scratch buffers of qk_block_indexmask_cuda (and the operators' work-queue scratch)."""
+    _scratch.clear()
+    cuda_attn.release_workspaces()
 
 
 def qk_block_indexmask_cuda(q, k, thresh, v=None):

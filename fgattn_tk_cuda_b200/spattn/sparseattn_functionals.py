@@ -41,10 +41,14 @@ def _sparse(out, query, key, value, mask, blocksz=128):
     """One sparse step.  A 4-tuple (kb_indices, kb_counts, max_q, denom) carries the max_q / denom of
     THESE query / key tensors and runs the non-renormalising block kernel; a pair of lists runs the
     renormalising kernel of its granularity (key blocks for blocksz 64, key tokens otherwise), which is
-    what a mask cached from an earlier diffusion run needs."""
+    what a mask cached from an earlier diffusion run needs; a 3-tuple (kb_indices, kb_counts, max_q) is
+    such a cached block mask together with the max_q of the run that built it, which the renormalising
+    persistent kernel takes as its per-row exponent hint."""
     q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
     if len(mask) == 4:
         spattn_interface.sp_attn_blocks_ml(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2], mask[3])
+    elif len(mask) == 3:
+        spattn_interface.sp_attn_blocks_hint(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2])
     elif blocksz == 64:
         spattn_interface.sp_attn_blocks(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
     else:
@@ -89,7 +93,8 @@ def compute_cache_and_attn_cuda(query, key, value, *args, **kwargs):
 def sparse_attn_from_cache_cuda(query, key, value, *args, **kwargs):
     """Sparse step from a cached mask (sparseattn_functionals.py:87-93)."""
     mask = kwargs["mask_cache"].get_mask_from_cache(kwargs.get("current_layer", 0))
-    return _sparse(_out(query), query, key, value, mask[:2], kwargs.get("blocksz", 128))
+    blocksz = kwargs.get("blocksz", 128)
+    return _sparse(_out(query), query, key, value, mask[:3] if blocksz == 64 else mask[:2], blocksz)
 
 
 def cached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
@@ -98,10 +103,13 @@ def cached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
     mask_cache = kwargs["mask_cache"]
     if mask_cache.run_fullattn(ditrun):
         out, *mask = compute_cache_and_attn_cuda(query, key, value, thresh=kwargs["thresh"], blocksz=kwargs["blocksz"])
-        mask_cache.update_cache(current_layer, *mask[:2])      # max_q / denom belong to this run's q, k only
+        # block mode keeps max_q with the lists: it belongs to this run's q, k, but on later runs it still
+        # places the exponent range of the renormalising kernel (denom is of no use there)
+        mask_cache.update_cache(current_layer, *mask[:3])
         return out
-    return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer)[:2],
-                   kwargs["blocksz"])
+    mask = mask_cache.get_mask_from_cache(current_layer)
+    blocksz = kwargs["blocksz"]
+    return _sparse(_out(query), query, key, value, mask[:3] if blocksz == 64 else mask[:2], blocksz)
 
 
 def bitmaskcached_attn_cuda(query, key, value, current_layer, ditrun, *args, **kwargs):
@@ -113,3 +121,11 @@ def bitmaskcached_attn_cuda(query, key, value, current_layer, ditrun, *args, **k
         mask_cache.update_cache(current_layer, mask, key.shape[2])
         return out
     return _sparse(_out(query), query, key, value, mask_cache.get_mask_from_cache(current_layer)[:2])
+
+
+def attn_2xmask_cuda(query, key, value, current_layer=None, ditrun=None, *args, **kwargs):
+    """Every other key, for every query block (sparseattn_functionals.py:137-153): the token-list kernel
+    at exactly half density, lists built on the fly."""
+    B, H, S, _ = query.shape
+    idx, cnt = mask_utils.halfindex_mask(B, H, S, kwargs.get("blocksz", 128), device=query.device)
+    return _sparse(_out(query), query, key, value, (idx, cnt))

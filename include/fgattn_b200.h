@@ -42,6 +42,12 @@ typedef enum {
 const char* fgattn_status_string(int status);
 /* cudaError_t of the most recent FGATTN_CUDA_ERROR on this thread. */
 int fgattn_last_cuda_error(void);
+/* Scheduling knobs, for tuning runs and tests; results never depend on them.  (No counterpart in the
+ * reference.)  "group_heads": (batch, head) units per group of the longest-first thread-block orders
+ * (0 = built-in choice, negative = back to the environment variable FGATTN_GROUP_HEADS, which is read
+ * once per process); "dense_persist": 1 / 0 forces the persistent / one-item form of the dense family,
+ * -1 = chosen by key length, below -1 = back to FGATTN_DENSE_PERSIST. */
+int fgattn_set_tuning(const char* name, int value);
 /* Synchronise `stream` and report whether any kernel launched through this library on the current
  * device gave up on a bounded wait.  Returns FGATTN_OK or FGATTN_DEVICE_TIMEOUT; *code (optional)
  * receives the id of the wait that ran out.  Clears the error word. */
@@ -147,9 +153,11 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
  * unit up to seq = kv_seq_len = 32768 fits; units are processed in as many head chunks as needed, and
  * a unit that does not fit returns FGATTN_SCRATCH_TOO_SMALL without launching anything.
  * Same arguments and results as fgattn_block_index_lists, minus the scratch pointer and with
- * kv_rows = seq (k / v as long as q).  It calls no
+ * kv_rows = seq (k / v as long as q: the k / v tensors MUST have exactly seq rows per head).  It calls no
  * cudaMalloc / cudaFree and no allocating library routine; bounded-wait time-outs go to the error
- * word that fgattn_check reads if some earlier call created it, else to a word inside the library.
+ * word that other entry points created if one exists, else to a word inside the library; fgattn_check
+ * reads both (and allocates nothing itself), so it reports a time-out of this entry point even when
+ * it is the only one ever called.
  * The first call on a device looks up the device address of the built-in array (once per device,
  * with that device current); make that first call outside any stream capture.
  * All calls share the one array and it keeps whatever the last call left in it (nothing in it needs
@@ -170,11 +178,27 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
                              int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
                              size_t workspace_bytes, void* stream);
 
-/* Bytes of device workspace fgattn_sp_attn_blocks_ml needs and fgattn_sp_attn_blocks / fgattn_sp_attn /
- * fgattn_booleanmask_128_listed can use
- * (work-queue counter + processing order of the query-block pairs).  The workspace is scratch: contents need not survive the call, but
- * two calls that may overlap on the device must not share it. */
+/* Bytes of device workspace fgattn_sp_attn_blocks_ml / fgattn_sp_attn_blocks_hint need and
+ * fgattn_sp_attn_blocks / fgattn_sp_attn / fgattn_booleanmask_128_listed can use (work-queue counter,
+ * processing order of the query-block pairs, re-run flags).  The workspace is scratch: contents need not
+ * survive the call, but two calls that may overlap on the device must not share it. */
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);
+
+/* fgattn_sp_attn_blocks (renormalising softmax over the kept key blocks, the sp_attn semantics of
+ * include/sparseattn_asyncgatherload_padded.cuh:198-249) at the speed of fgattn_sp_attn_blocks_ml, for
+ * the case the reference replays most: lists cached from an earlier diffusion step meet new q, k
+ * (python/spattn/sparseattn_functionals.py:110-113).  max_q_hint (fp32 [B,H,1,S_pad], the max_q layout)
+ * is a per-row ESTIMATE of max_j q_i.k_j over the listed keys -- typically the max_q that
+ * fgattn_block_index_lists wrote when the lists were built.  It only positions the exponent range
+ * (the result does not depend on it): an estimate within about +-60/(scale*log2 e) of the true row
+ * maximum is good; rows for which it is not (their probability sum overflows or underflows) are
+ * detected and their query blocks are recomputed by the running-maximum kernel of
+ * fgattn_sp_attn_blocks inside the same call, so the result is always that of fgattn_sp_attn_blocks
+ * within rounding.  `workspace` as for fgattn_sp_attn_blocks_ml (required). */
+int fgattn_sp_attn_blocks_hint(void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                               const int* kb_counts, int list_stride, const float* max_q_hint, int batch, int heads,
+                               int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
+                               size_t workspace_bytes, void* stream);
 
 /* Block-sparse attention with the renormalising softmax of the sp_attn operator (softmax over the kept
  * keys only, include/sparseattn_asyncgatherload_padded.cuh:198-249) on key-block lists.  `workspace`
@@ -227,6 +251,15 @@ size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int block
 int fgattn_topk_indices(int* kv_indices, int* kv_num_indices, int list_stride, const void* q, const void* k,
                         int select_k, int batch, int heads, int seq, int D, int blocksz, int kv_rows, int kv_seq_len,
                         float scale, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- self-test ------------------------------------------------------------------------------- */
+
+/* Launches one warp that waits, with a budget of budget_cycles clock cycles (1 .. 1e8), on an mbarrier
+ * nobody arrives at.  The wait gives up, the kernel returns normally and the next fgattn_check on the
+ * stream reports FGATTN_DEVICE_TIMEOUT with code 9001: the path every kernel of this library takes when
+ * one of its bounded waits runs out, exercised without disturbing the GPU.  (The reference's kernels
+ * wait without bound -- include/fullattn_tma.cuh:152-158 -- so it has nothing of the kind.) */
+int fgattn_selftest_bounded_wait(long long budget_cycles, void* stream);
 
 #ifdef __cplusplus
 }

@@ -182,16 +182,21 @@ def test_identity_lists_equal_dense():
         assert d.max().item() <= 8e-3 and d.mean().item() <= 5e-4, (fn, d.max().item(), d.mean().item())
 
 
-@pytest.mark.parametrize("group", ["1", "2", None])
-def test_thread_block_order_with_several_head_groups(monkeypatch, group):
-    """The longest-first order is built per group of heads (FGATTN_GROUP_HEADS overrides the group size);
-    whatever the grouping, every item must be visited exactly once: same output as storage order."""
+@pytest.mark.parametrize("group", [1, 2, 0])
+def test_thread_block_order_with_several_head_groups(group):
+    """The longest-first order is built per group of heads (the "group_heads" tuning knob overrides the
+    group size; 0 = built-in choice); whatever the grouping, every item must be visited exactly once:
+    same output as storage order."""
     from oracle import fgattn_oracle as orc
     capi = _capi()
-    if group is None:
-        monkeypatch.delenv("FGATTN_GROUP_HEADS", raising=False)
-    else:
-        monkeypatch.setenv("FGATTN_GROUP_HEADS", group)
+    capi.set_tuning("group_heads", group)
+    try:
+        _order_case(capi, orc)
+    finally:
+        capi.set_tuning("group_heads", -1)
+
+
+def _order_case(capi, orc):
     B, H, S, D = 1, 5, 1500, 64
     nqb = nkb = (S + 63) // 64
     g = torch.Generator().manual_seed(77)

@@ -60,3 +60,48 @@ def test_noalloc_rejects_units_beyond_the_builtin_scratch():
     st = lib.fgattn_block_index_lists_noalloc(buf, buf, 625, buf, buf, None, buf, buf, None, 1e-3, 1, 1, S, 128, S,
                                               0.0, None)
     assert st == 7 and b"scratch" in lib.fgattn_status_string(st)
+
+
+_FIRST_CALL_SCRIPT = r"""
+import torch
+from fgattn_tk_cuda_b200 import capi, synth
+w = synth.Workload("na0", 1, 2, 900, 128, "clustered", centroids=8, run=64, tau=1e-3, seed=79)
+q, k, v = (t.cuda() for t in synth.make_qkv(w))
+B, H, S, D = q.shape
+nqb = nkb = (S + 63) // 64
+s_pad = 128 * ((S + 127) // 128)
+def bufs():
+    return (torch.full((B, H, nqb, nkb), -7, dtype=torch.int32, device="cuda"),
+            torch.full((B, H, nqb), -7, dtype=torch.int32, device="cuda"),
+            torch.full((B, H, 1, s_pad), 3.0, device="cuda"), torch.full((B, H, 1, s_pad), 3.0, device="cuda"))
+got = bufs()
+scratch = torch.empty(capi.block_scratch_bytes(B, H, S) // 4, device="cuda")     # allocated BEFORE, by the caller
+torch.cuda.synchronize()
+# the very first call into the library in this process is the allocation-free one
+capi.block_index_lists_noalloc(*got, q, k, w.tau)
+torch.cuda.synchronize()
+free0 = torch.cuda.mem_get_info()[0]
+capi.check()                                   # reads the word built into the library; allocates nothing
+free1 = torch.cuda.mem_get_info()[0]
+assert free0 - free1 < (1 << 20), (free0, free1)
+ref = bufs()
+capi.block_index_lists(*ref, q, k, w.tau, scratch)
+capi.check()
+for a, b in zip(ref, got):
+    assert torch.equal(a, b)
+print("first-call ok")
+"""
+
+
+def test_noalloc_as_first_call_of_a_fresh_process():
+    """A process whose first and only use of the library is the allocation-free entry point: the
+    results are right and fgattn_check -- which then has only the library's built-in error word to
+    read -- reports a clean run without allocating anything itself."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, "-c", _FIRST_CALL_SCRIPT], cwd=root, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "first-call ok" in r.stdout
