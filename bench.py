@@ -400,6 +400,11 @@ def main():
         del kidx, tk_scratch, tcnt
         # replay of a cached mask: the renormalising block kernel on the same key-block lists
         ms_renorm = ev_time(lambda: ops.sp_attn_blocks(o, q, k, v, idx, cnt), 10, 3)
+        # the same replay on the persistent kernel: the cached max_q of the list build as the exponent hint,
+        # queries that have moved on since (the lists and the hint are stale by one step)
+        q_next = (q.float() * 1.03 + 0.01).to(torch.bfloat16)
+        ms_hint = ev_time(lambda: ops.sp_attn_blocks_hint(o, q_next, k, v, idx, cnt, max_q), 20, 3)
+        del q_next
         stages = {
             "full_attn_ms": ms_full, "full_attn_tflops": F_full / ms_full / 1e9,
             "full_attn_frac_of_peak": F_full / ms_full / 1e9 / peak,
@@ -422,6 +427,8 @@ def main():
             "sp_attn_blocks_renorm_ms": ms_renorm,
             "sp_attn_blocks_renorm_tflops_on_kept_blocks": F_sparse / ms_renorm / 1e9,
             "sp_attn_blocks_renorm_frac_of_peak": F_sparse / ms_renorm / 1e9 / peak,
+            "sp_attn_blocks_hint_ms": ms_hint, "sp_attn_blocks_hint_tflops_on_kept_blocks": F_sparse / ms_hint / 1e9,
+            "sp_attn_blocks_hint_frac_of_peak": F_sparse / ms_hint / 1e9 / peak,
             "dense_plus_lists_ms": ms_build, "dense_plus_lists_tflops": F_full / ms_build / 1e9,
         }
         # re-build the lists that the stage timings overwrote with equal content (same inputs)
@@ -619,6 +626,7 @@ def main():
         ms_l = ev_time(lambda: capi.block_index_lists(i4, n4, m4, l4, q4, k4, c4.tau, sc4), 5, 2)
         ms_s = ev_time(lambda: ops.sp_attn_blocks_ml(o4, q4, k4, v4, i4, n4, m4, l4), 20, 3)
         ms_r = ev_time(lambda: ops.sp_attn_blocks(o4, q4, k4, v4, i4, n4), 10, 3)
+        ms_h = ev_time(lambda: ops.sp_attn_blocks_hint(o4, q4, k4, v4, i4, n4, m4), 20, 3)
         d4 = nnz4 / (c4.B * c4.H * nb4 * nb4)
         configs["c4_ragged"] = {"workload": c4.name, "density": d4, "full_attn_ms": ms_f,
                                 "full_attn_tflops": F4 / ms_f / 1e9, "full_attn_frac_of_peak": F4 / ms_f / 1e9 / peak,
@@ -626,6 +634,7 @@ def main():
                                 "sparse_ms": ms_s, "sparse_tflops_on_kept_blocks": Fs4 / ms_s / 1e9,
                                 "sparse_frac_of_peak": Fs4 / ms_s / 1e9 / peak,
                                 "sparse_renorm_ms": ms_r, "sparse_renorm_tflops_on_kept_blocks": Fs4 / ms_r / 1e9,
+                                "sparse_hint_ms": ms_h, "sparse_hint_tflops_on_kept_blocks": Fs4 / ms_h / 1e9,
                                 "sparse_speedup_over_full": ms_f / ms_s, "speedup_gap": (1.0 / d4) / (ms_f / ms_s),
                                 "union_overhead": union_overhead(i4, n4, nb4)}
         capi.check()

@@ -234,22 +234,26 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
     FG_CUDA(cudaGetLastError());
     p.order = ws + 4;
   }
-  dim3 grid(n_units * p.quads, 1, 1);
-  if (D == 128) {
-    const int smem = fg::SparseCfg<128>::smem_bytes(p.list_cap, p.nkb);
-    if (smem > 232448) return FGATTN_UNSUPPORTED;
-    auto kern = fg::sparse_block_attn_kernel<128>;
-    r = set_smem(kern, smem);
+  p.n_total = n_units * p.quads;
+  int n_ctas = p.n_total;                       // one CTA per item; the re-run pass: at most one per SM
+  if (redo) {
+    int sms = 0;
+    r = sm_count(&sms);
     if (r) return r;
-    kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
-  } else {
-    const int smem = fg::SparseCfg<64>::smem_bytes(p.list_cap, p.nkb);
-    if (smem > 232448) return FGATTN_UNSUPPORTED;
-    auto kern = fg::sparse_block_attn_kernel<64>;
-    r = set_smem(kern, smem);
-    if (r) return r;
-    kern<<<grid, 384, smem, st>>>(mq, mk, mv, p);
+    n_ctas = std::min(p.n_total, sms);
   }
+  const int smem = (D == 128) ? fg::SparseCfg<128>::smem_bytes(p.list_cap, p.nkb)
+                              : fg::SparseCfg<64>::smem_bytes(p.list_cap, p.nkb);
+  if (smem > 232448) return FGATTN_UNSUPPORTED;
+  auto go = [&](auto kern) -> int {
+    int rr = set_smem(kern, smem);
+    if (rr) return rr;
+    kern<<<dim3(n_ctas, 1, 1), 384, smem, st>>>(mq, mk, mv, p);
+    return FGATTN_OK;
+  };
+  if (D == 128) r = redo ? go(fg::sparse_block_attn_kernel<128, true>) : go(fg::sparse_block_attn_kernel<128, false>);
+  else r = redo ? go(fg::sparse_block_attn_kernel<64, true>) : go(fg::sparse_block_attn_kernel<64, false>);
+  if (r) return r;
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;
 }

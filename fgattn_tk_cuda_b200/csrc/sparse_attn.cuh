@@ -27,11 +27,11 @@ struct SparseParams {
   // 64-row query blocks.  An order with the long lists first keeps the end of the launch short.
   const int* order;
   int quads;
-  // Re-run pass behind the fixed-offset persistent kernel: redo[unit * npairs + pair] != 0 marks a pair of
-  // query blocks (128 rows) whose rows left the safe exponent range there; a CTA whose two pairs are both
-  // unmarked returns at once.  Null = every item is computed.
+  // Re-run pass behind the fixed-offset persistent kernel (template parameter REDO): redo[unit * npairs +
+  // pair] != 0 marks a pair of query blocks (128 rows) whose rows left the safe exponent range there.  A few
+  // CTAs (one per SM at most) walk all n_total items and compute the ones with a marked pair.
   const int* redo;
-  int npairs;
+  int npairs, n_total;
   float scale_log2;
 };
 
@@ -57,13 +57,14 @@ enum : int {
   SB_S_FULL = 17,   // +slot
   SB_P_FULL = 19,   // +slot
   SB_O_FULL = 21,   // +slot
-  SB_COUNT = 23
+  SB_DONE = 23,     // REDO: every product of the item has been executed (barriers are set up anew per item)
+  SB_COUNT = 24
 };
 
 // entry = key block index | (kept by rows 0-63) << 30 | (kept by rows 64-127) << 31
 __device__ __forceinline__ int entry_kb(uint32_t e) { return int(e & 0x3FFFFFFFu); }
 
-template <int D>
+template <int D, bool REDO>
 __global__ void __launch_bounds__(384, 1)
 sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                          const __grid_constant__ CUtensorMap mv, const SparseParams p) {
@@ -80,17 +81,41 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
   uint32_t* bitmaps = lists + 2 * p.list_cap;                                                          // [2][2][words]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int item = p.order ? p.order[blockIdx.x] : int(blockIdx.x);
+  const int words = (p.nkb + 31) / 32;
+  // REDO: does item `it` (a quad = two pairs of query blocks) hold a marked pair?
+  auto marked = [&](int it) -> bool {
+    const int u = it / p.quads, pr = (it - u * p.quads) * 2;
+    const int* f = p.redo + size_t(u) * p.npairs + pr;
+    return f[0] != 0 || (pr + 1 < p.npairs && f[1] != 0);
+  };
+  if constexpr (REDO) {
+    // the common case is that nothing at all is marked: leave before any set-up (CTA-uniform)
+    bool any = false;
+    for (int it = blockIdx.x; it < p.n_total && !any; it += gridDim.x) any = marked(it);
+    if (!any) return;
+  }
+  if (warp == 8) {
+    __syncwarp();
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  bool first_item = true;
+  for (int iter = blockIdx.x;; iter += gridDim.x) {
+  int item;
+  if constexpr (REDO) {
+    if (iter >= p.n_total) break;
+    if (!marked(iter)) continue;
+    item = iter;
+  } else {
+    item = p.order ? p.order[blockIdx.x] : int(blockIdx.x);
+  }
   const int bh = item / p.quads;
   const int q0 = (item - bh * p.quads) * 256;
-  const int words = (p.nkb + 31) / 32;
-  if (p.redo) {
-    const int pr = (item - bh * p.quads) * 2;
-    const int* f = p.redo + size_t(bh) * p.npairs + pr;
-    if (f[0] == 0 && (pr + 1 >= p.npairs || f[1] == 0)) return;       // CTA-uniform: nothing to re-run here
-  }
 
   if (tid == 0) {
+    if (REDO && !first_item) {
+      for (int i = 0; i < SB_COUNT; ++i) mbar_inval(bar(i));
+    }
     ab->flag = 0;
     mbar_init(bar(SB_Q_FULL), 1);
     for (int s = 0; s < 8; ++s) {
@@ -102,12 +127,8 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
       mbar_init(bar(SB_P_FULL + t), 128);
       mbar_init(bar(SB_O_FULL + t), 1);
     }
+    mbar_init(bar(SB_DONE), 1);
     mbar_fence_init();
-  }
-  if (warp == 8) {
-    __syncwarp();
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
   }
   // ---- union of the two query blocks' lists, one warp per slot (warps 0 and 4)
   if ((warp & 3) == 0 && warp < 8) {
@@ -170,7 +191,7 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
-    reg_dealloc<72>();
+    if (first_item) reg_dealloc<72>();
     if (lane == 0) {
       tma_prefetch_desc(&mq);
       tma_prefetch_desc(&mk);
@@ -214,7 +235,7 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ UMMA issuer
-    reg_dealloc<72>();
+    if (first_item) reg_dealloc<72>();
     {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
@@ -263,10 +284,17 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
           }
         }
       }
+      if constexpr (REDO) {
+        // the barriers are torn down after this item: every commit issued above must have landed first
+        if (ok) {
+          umma_commit_elect(bar(SB_DONE));
+          ok = mbar_wait_warp(bar(SB_DONE), 0, ab, p.err, 505);
+        }
+      }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ softmax warpgroups
-    reg_alloc<216>();
+    if (first_item) reg_alloc<216>();
     const int t = warp >> 2, wq = warp & 3, half = wq >> 1;
     const int row = q0 + t * 128 + wq * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
@@ -305,13 +333,20 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
     }
   }
   else {
-    reg_dealloc<72>();
+    if (first_item) reg_dealloc<72>();
+  }
+  if constexpr (!REDO) break;
+  first_item = false;
+  const bool aborted = ab->flag != 0;
+  tc_fence_before();
+  __syncthreads();                     // the item is complete: its barriers and lists may be reused
+  if (aborted) break;                  // a wait ran out: no further items
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 8) {
     __syncwarp();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(*tmem_slot, 512);
   }
 }
 
