@@ -44,6 +44,7 @@ PROTOTYPES = {
     "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                       _vp]),
     "fgattn_sp_attn_workspace_bytes": (_sz, [_i, _i, _i]),
+    "fgattn_sp_attn_token_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "fgattn_sp_attn_blocks_hint": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
                                         _vp]),
     "fgattn_selftest_bounded_wait": (_i, [_ll, _vp]),
@@ -184,13 +185,20 @@ def all_index_mask(kv_indices, kv_num_indices, batch, heads, seqblocks, seq):
               kv_indices.shape[3], _stream(kv_indices))
 
 
-def sp_attn(o, q, k, v, kv_indices, kv_num_indices, scale=0.0, workspace=None, ordered=True):
+def sp_attn_token_workspace_bytes(B, H, S, kv_rows) -> int:
+    return int(lib().fgattn_sp_attn_token_workspace_bytes(B, H, S, kv_rows))
+
+
+def sp_attn(o, q, k, v, kv_indices, kv_num_indices, scale=0.0, workspace=None, ordered=True, block_route=False):
     """ordered: thread blocks take the longest lists first (needs the workspace, allocated here when not
-    given); ordered=False runs them in storage order with no workspace."""
+    given); ordered=False runs them in storage order with no workspace.  block_route (with ordered):
+    allocate the large workspace, with which -- once set_tuning("token_block_route", 1) is on -- query
+    blocks whose lists fill the key blocks they touch load whole K/V tiles instead of gathering rows."""
     _check_qkv(o, q, k, v)
     B, H, S, D = q.shape
     if ordered and workspace is None:
-        workspace = torch.empty(sp_attn_workspace_bytes(B, H, S), dtype=torch.uint8, device=q.device)
+        nbytes = sp_attn_token_workspace_bytes(B, H, S, k.shape[2]) if block_route else sp_attn_workspace_bytes(B, H, S)
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     ws_ptr = _ptr(workspace) if ordered else None
     ws_bytes = workspace.numel() * workspace.element_size() if ordered else 0
     with torch.cuda.device(q.device):

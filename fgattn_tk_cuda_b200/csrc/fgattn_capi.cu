@@ -16,6 +16,7 @@
 #include "sparse_ml_persistent.cuh"
 #include "sparse_token_attn.cuh"
 #include "tensor_map.h"
+#include "token_blocks.cuh"
 #include "topk_select.cuh"
 
 // Scratch and error word of the allocation-free entry point live in the library image.  In host code
@@ -68,12 +69,21 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // the persistent / one-item form of the dense family; -1 = by key length).
 // fgattn_set_tuning overrides either for the rest of the process.
 constexpr int kTuningUnset = -2147483647 - 1;
-std::atomic<int> g_tune_group_heads{kTuningUnset}, g_tune_dense_persist{kTuningUnset};
+std::atomic<int> g_tune_group_heads{kTuningUnset}, g_tune_dense_persist{kTuningUnset}, g_tune_token_route{kTuningUnset};
 int env_group_heads() {
   const int t = g_tune_group_heads.load(std::memory_order_relaxed);
   if (t != kTuningUnset) return t;
   static const int v = [] { const char* e = getenv("FGATTN_GROUP_HEADS"); return e ? atoi(e) : 0; }();
   return v;
+}
+// FGATTN_TOKEN_BLOCK_ROUTE=1 lets the token-list operator send query blocks with well-filled lists through
+// whole K/V tiles (off by default: threshold-mask lists fill only 55-60 % of the blocks they touch, and for
+// them the conversion costs more than it saves)
+bool env_token_block_route() {
+  const int t = g_tune_token_route.load(std::memory_order_relaxed);
+  if (t != kTuningUnset) return t != 0;
+  static const int v = [] { const char* e = getenv("FGATTN_TOKEN_BLOCK_ROUTE"); return e ? atoi(e) : 0; }();
+  return v != 0;
 }
 int env_dense_persist() {
   const int t = g_tune_dense_persist.load(std::memory_order_relaxed);
@@ -188,7 +198,8 @@ int dense_setup(DenseSetup& s, const void* q, const void* k, const void* v, int 
 // `redo` (optional, [B*H * ceil(S/128)] flags): re-run pass, only the marked pairs of query blocks are computed.
 int launch_sparse(void* o, const void* q, const void* k, const void* v, const int* kb_idx, const int* kb_cnt,
                   int list_stride, int B, int H, int S, int D, int kv_rows, int kv_len, float scale, void* workspace,
-                  size_t workspace_bytes, cudaStream_t st, const int* redo = nullptr) {
+                  size_t workspace_bytes, cudaStream_t st, const int* redo = nullptr,
+                  const unsigned long long* kb_mask = nullptr) {
   int r = check_qk(q, k, B, H, S, D, kv_rows, kv_len);
   if (r) return r;
   if (!o || !v || !kb_idx || !kb_cnt) return FGATTN_INVALID_ARGUMENT;
@@ -217,6 +228,7 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
     return fg::encode_tiled_fn() ? FGATTN_INVALID_ARGUMENT : FGATTN_NO_DRIVER;
   p.quads = (S + 255) / 256;
   p.redo = redo;
+  p.kb_mask = kb_mask;                   // token-derived lists: one list (with column masks) per 128-row block
   p.npairs = (S + 127) / 128;
   const int n_units = B * H;
   if ((long long)n_units * p.quads > 2147483647LL) return FGATTN_UNSUPPORTED;
@@ -258,9 +270,19 @@ int launch_sparse(void* o, const void* q, const void* k, const void* v, const in
   return FGATTN_OK;
 }
 
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
 }  // namespace
 
 extern "C" {
+
+namespace {
+int launch_sparse_persistent(bool renorm, void* o, const void* q, const void* k, const void* v, const int* kb_indices,
+                             const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
+                             int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
+                             size_t workspace_bytes, void* stream, const unsigned long long* kb_mask = nullptr,
+                             const int* route = nullptr);
+}  // namespace
 
 const char* fgattn_status_string(int status) {
   switch (status) {
@@ -282,6 +304,7 @@ int fgattn_set_tuning(const char* name, int value) {
   if (!name) return FGATTN_INVALID_ARGUMENT;
   if (!strcmp(name, "group_heads")) g_tune_group_heads.store(value < 0 ? kTuningUnset : value);
   else if (!strcmp(name, "dense_persist")) g_tune_dense_persist.store(value < -1 ? kTuningUnset : value);
+  else if (!strcmp(name, "token_block_route")) g_tune_token_route.store(value < 0 ? kTuningUnset : value);
   else return FGATTN_INVALID_ARGUMENT;
   return FGATTN_OK;
 }
@@ -473,6 +496,57 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
   p.pairs = (seq + 255) / 256;
   const int n_units = batch * heads;
   if ((long long)n_units * p.pairs > 2147483647LL) return FGATTN_UNSUPPORTED;
+  // ---- block route: with the large workspace, query blocks whose lists nearly fill the 64-key blocks they
+  // touch are computed from whole K/V tiles (TMA by block index, unlisted columns switched off) on the
+  // persistent fixed-offset kernel; the others stay on the row gather below
+  const int nkb = (kv_rows + 63) / 64, nqb = p.nqb, s_pad = nqb * 128;
+  const size_t pre_smem = fg::token_blocks_smem_bytes(nkb, D);
+  const int ml_smem = (D == 128) ? fg::SparseMLCfg<128>::smem_bytes(nkb + 2, nkb) : fg::SparseMLCfg<64>::smem_bytes(nkb + 2, nkb);
+  const int two_smem = (D == 128) ? fg::SparseCfg<128>::smem_bytes(nkb + 2, nkb) : fg::SparseCfg<64>::smem_bytes(nkb + 2, nkb);
+  const bool block_route = workspace && workspace_bytes >= fgattn_sp_attn_token_workspace_bytes(batch, heads, seq, kv_rows) &&
+                           pre_smem <= 48 * 1024 && ml_smem <= 232448 && two_smem <= 232448 && env_token_block_route();
+  if (block_route) {
+    char* base = static_cast<char*>(workspace);
+    const size_t small = align256(fgattn_sp_attn_workspace_bytes(batch, heads, seq));
+    const size_t n_rows = size_t(n_units) * nqb;
+    char* w_ml = base + small;                                   // queue / order / re-run flags of the block route
+    int* kb_cnt2 = reinterpret_cast<int*>(base + 2 * small);
+    int* route = reinterpret_cast<int*>(base + 2 * small + align256(n_rows * 4));
+    float* hint = reinterpret_cast<float*>(base + 2 * small + 2 * align256(n_rows * 4));
+    int* kb_idx2 = reinterpret_cast<int*>(reinterpret_cast<char*>(hint) + align256(size_t(n_units) * s_pad * 4));
+    unsigned long long* kb_mask2 =
+        reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(kb_idx2) + align256(n_rows * nkb * 4));
+    fg::TokenBlocksParams tb;
+    memset(&tb, 0, sizeof(tb));
+    tb.kv_idx = kv_indices;
+    tb.kv_cnt = kv_num_indices;
+    tb.q = static_cast<const __nv_bfloat16*>(q);
+    tb.k = static_cast<const __nv_bfloat16*>(k);
+    tb.kb_idx = kb_idx2;
+    tb.kb_mask = kb_mask2;
+    tb.kb_cnt = kb_cnt2;
+    tb.route = route;
+    tb.hint = hint;
+    tb.S = seq;
+    tb.S_pad = s_pad;
+    tb.S_kv = kv_rows;
+    tb.nqb = nqb;
+    tb.nkb = nkb;
+    tb.mask_stride = mask_stride;
+    tb.kb_stride = nkb;
+    // whole tiles pay when the listed columns fill most of them: the block route computes every column of
+    // a touched block at about 1.5 times the row gather's rate per column
+    tb.fill_min = 0.75f;
+    // the sampled maximum is a lower estimate of the row maximum: shift the exponent window up by 2^20
+    tb.hint_margin = 20.0f / p.scale_log2;
+    if (D == 128) fg::token_lists_to_blocks_kernel<128><<<dim3(nqb, n_units), 256, pre_smem, st>>>(tb);
+    else fg::token_lists_to_blocks_kernel<64><<<dim3(nqb, n_units), 256, pre_smem, st>>>(tb);
+    FG_CUDA(cudaGetLastError());
+    r = launch_sparse_persistent(true, o, q, k, v, kb_idx2, kb_cnt2, nkb, hint, nullptr, batch, heads, seq, D, kv_rows,
+                                 kv_rows, scale, w_ml, small, stream, kb_mask2, route);
+    if (r) return r;
+    p.route = route;
+  }
   if (workspace) {
     // thread-block order: inside groups of units, longest lists first.  The row gather gains little from
     // L2 residency of K/V, and large groups balance better (measured at (1,12,32760,128): 0.90 ms in
@@ -505,6 +579,16 @@ int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const i
   }
   FG_CUDA(cudaGetLastError());
   return FGATTN_OK;
+}
+
+size_t fgattn_sp_attn_token_workspace_bytes(int batch, int heads, int seq, int kv_rows) {
+  if (batch <= 0 || heads <= 0 || seq <= 0 || kv_rows <= 0) return 0;
+  // two queue / order regions (block route and row gather), then per query block: touched-block count and
+  // route flag; per query row: exponent hint; per (query block, key block): block index and column mask
+  const size_t small = align256(fgattn_sp_attn_workspace_bytes(batch, heads, seq));
+  const size_t nqb = size_t((seq + 127) / 128), nkb = size_t((kv_rows + 63) / 64), bh = size_t(batch) * heads;
+  return 2 * small + 2 * align256(bh * nqb * 4) + align256(bh * nqb * 128 * 4) + align256(bh * nqb * nkb * 4) +
+         align256(bh * nqb * nkb * 8);
 }
 
 size_t fgattn_block_scratch_bytes(int batch, int heads, int seq, int kv_seq_len) {
@@ -640,7 +724,8 @@ namespace {
 int launch_sparse_persistent(bool renorm, void* o, const void* q, const void* k, const void* v, const int* kb_indices,
                              const int* kb_counts, int list_stride, const float* max_q, const float* denom, int batch,
                              int heads, int seq, int D, int kv_rows, int kv_seq_len, float scale, void* workspace,
-                             size_t workspace_bytes, void* stream) {
+                             size_t workspace_bytes, void* stream, const unsigned long long* kb_mask,
+                             const int* route) {
   int r = check_qk(q, k, batch, heads, seq, D, kv_rows, kv_seq_len);
   if (r) return r;
   if (!o || !v || !kb_indices || !kb_counts || !max_q || (!renorm && !denom) || !workspace || list_stride < 1)
@@ -655,6 +740,8 @@ int launch_sparse_persistent(bool renorm, void* o, const void* q, const void* k,
   p.denom = denom;
   p.kb_idx = kb_indices;
   p.kb_cnt = kb_counts;
+  p.kb_mask = kb_mask;
+  p.route = route;
   p.S = seq;
   p.S_pad = ((seq + 127) / 128) * 128;
   p.kv_len = kv_seq_len;
@@ -683,23 +770,22 @@ int launch_sparse_persistent(bool renorm, void* o, const void* q, const void* k,
   int sms = 0;
   r = sm_count(&sms);
   if (r) return r;
-  // heads per queue group: enough items to balance the SMs (about six per SM), K/V of a group <= 64 MiB
+  // Queue order: units in groups whose K/V (<= 56 MiB) stays in L2, longest items first inside a group.
+  // The end of the launch is made of the last group's short items, and a small last group runs out of
+  // them while long items are still going, so the last group also takes the remainder (it holds between
+  // one and two groups' worth of units) and a launch with few items per SM is one single group
+  // (measured on the first 16 heads of C3: 0.39 ms in groups of 6,6,4 heads, 0.34 ms as one group).
   const int n_units = batch * heads;
   const size_t kv_bytes_per_unit = size_t(4) * kv_rows * D;
-  int group_heads = (6 * sms + p.npairs - 1) / p.npairs;
-  group_heads = std::min<int>(group_heads, int(std::max<size_t>(1, (size_t(64) << 20) / kv_bytes_per_unit)));
+  int group_heads = int(std::max<size_t>(1, (size_t(56) << 20) / kv_bytes_per_unit));
+  if (p.n_items < 16 * sms) group_heads = n_units;
   if (env_group_heads() > 0) group_heads = env_group_heads();            // tuning override
   group_heads = std::max(1, std::min(group_heads, n_units));
-  {
-    // groups of equal size: a short last group would start its long items late and leave SMs idle at the
-    // end of the launch (dispatch simulation on the C3 lists: 2 % above the ideal makespan with groups of
-    // 7,7,7,7,4 heads, 0.3 % with 8,8,8,8; 15 % against 0.6 % for half the heads)
-    const int n_groups = (n_units + group_heads - 1) / group_heads;
-    group_heads = (n_units + n_groups - 1) / n_groups;
-  }
-  fg::sparse_order_kernel<<<(n_units + group_heads - 1) / group_heads, 256, 0, st>>>(
-      kb_counts, static_cast<int*>(workspace) + 4, p.queue, p.nqb, p.npairs, n_units, group_heads, 1, 2, 0,
-      renorm ? p.redo : nullptr);
+  const int n_groups = std::max(1, n_units / group_heads);
+  // an item is a pair of 64-row query blocks with one list each, or (token-derived lists) one 128-row block
+  fg::sparse_order_kernel<<<n_groups, 256, 0, st>>>(
+      kb_counts, static_cast<int*>(workspace) + 4, p.queue, kb_mask ? p.npairs : p.nqb, p.npairs, n_units, group_heads, 1,
+      kb_mask ? 1 : 2, 0, renorm ? p.redo : nullptr);
   FG_CUDA(cudaGetLastError());
   const int grid = std::min(p.n_items, sms);
   const int smem = (D == 128) ? fg::SparseMLCfg<128>::smem_bytes(p.list_cap, p.nkb)
@@ -711,17 +797,20 @@ int launch_sparse_persistent(bool renorm, void* o, const void* q, const void* k,
     kern<<<grid, threads, smem, st>>>(mq, mk, mv, p);
     return FGATTN_OK;
   };
+  if (kb_mask && !renorm) return FGATTN_INVALID_ARGUMENT;      // token-derived lists exist in the renormalising form only
   if (D == 128)
-    r = renorm ? go(fg::sparse_ml_persistent_kernel<128, true>, fg::SparseMLCfg<128>::kThreads)
-               : go(fg::sparse_ml_persistent_kernel<128, false>, fg::SparseMLCfg<128>::kThreads);
+    r = kb_mask ? go(fg::sparse_ml_persistent_kernel<128, true, true>, fg::SparseMLCfg<128>::kThreads)
+        : renorm ? go(fg::sparse_ml_persistent_kernel<128, true>, fg::SparseMLCfg<128>::kThreads)
+                 : go(fg::sparse_ml_persistent_kernel<128, false>, fg::SparseMLCfg<128>::kThreads);
   else
-    r = renorm ? go(fg::sparse_ml_persistent_kernel<64, true>, fg::SparseMLCfg<64>::kThreads)
-               : go(fg::sparse_ml_persistent_kernel<64, false>, fg::SparseMLCfg<64>::kThreads);
+    r = kb_mask ? go(fg::sparse_ml_persistent_kernel<64, true, true>, fg::SparseMLCfg<64>::kThreads)
+        : renorm ? go(fg::sparse_ml_persistent_kernel<64, true>, fg::SparseMLCfg<64>::kThreads)
+                 : go(fg::sparse_ml_persistent_kernel<64, false>, fg::SparseMLCfg<64>::kThreads);
   if (r) return r;
   FG_CUDA(cudaGetLastError());
   if (renorm)   // items whose rows left the safe exponent range run again with the running maximum
     return launch_sparse(o, q, k, v, kb_indices, kb_counts, list_stride, batch, heads, seq, D, kv_rows, kv_seq_len,
-                         scale, nullptr, 0, st, p.redo);
+                         scale, nullptr, 0, st, p.redo, kb_mask);
   return FGATTN_OK;
 }
 }  // namespace
@@ -819,10 +908,6 @@ int fgattn_sp_attn_blocks(void* o, const void* q, const void* k, const void* v, 
 }
 
 // ---- top-k selector ------------------------------------------------------------------------------
-namespace {
-size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
-}  // namespace
-
 size_t fgattn_topk_scratch_bytes(int batch, int heads, int seq, int D, int blocksz, int kv_seq_len) {
   if (batch <= 0 || heads <= 0 || seq <= 0 || D <= 0 || blocksz <= 0 || kv_seq_len <= 0) return 0;
   const size_t bh = size_t(batch) * heads, nblk = size_t((seq + blocksz - 1) / blocksz);

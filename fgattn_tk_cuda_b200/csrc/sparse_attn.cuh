@@ -32,6 +32,9 @@ struct SparseParams {
   // CTAs (one per SM at most) walk all n_total items and compute the ones with a marked pair.
   const int* redo;
   int npairs, n_total;
+  // Token-derived lists (null = key-block lists of 64-row query blocks): one list per 128-row query block,
+  // [BH, npairs, list_stride] ascending key blocks, with the live columns of every listed block in kb_mask.
+  const unsigned long long* kb_mask;
   float scale_log2;
 };
 
@@ -137,11 +140,12 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
     uint32_t* bm1 = bitmaps + (t * 2 + 1) * words;
     for (int w = lane; w < 2 * words; w += 32) bm0[w] = 0u;      // bm0 and bm1 are adjacent
     __syncwarp();
+    const int list_rows = p.kb_mask ? p.npairs : p.nqb;
     for (int half = 0; half < 2; ++half) {
-      const int qb = (q0 >> 6) + t * 2 + half;
-      if (qb < p.nqb) {
-        const int* src = p.kb_idx + (size_t(bh) * p.nqb + qb) * p.list_stride;
-        const int n = min(p.kb_cnt[size_t(bh) * p.nqb + qb], p.list_stride);
+      const int qb = p.kb_mask ? (q0 >> 7) + t : (q0 >> 6) + t * 2 + half;   // token lists: one list for both halves
+      if (qb < list_rows) {
+        const int* src = p.kb_idx + (size_t(bh) * list_rows + qb) * p.list_stride;
+        const int n = min(p.kb_cnt[size_t(bh) * list_rows + qb], p.list_stride);
         uint32_t* bm = half ? bm1 : bm0;
         for (int i = lane; i < n; i += 32) {
           const int kb = src[i];
@@ -305,15 +309,26 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
     OnlineState st;
     online_init(st);
     bool ok = true;
+    // token-derived lists: entry i of the slot's list has column mask i (the list is the block's own)
+    const unsigned long long* masks =
+        p.kb_mask ? p.kb_mask + (size_t(bh) * p.npairs + (q0 >> 7) + t) * p.list_stride : nullptr;
     for (int j = 0; j < nt; ++j) {
       const uint32_t e0 = list[2 * j], e1 = list[2 * j + 1];
       const int valid0 = ((e0 >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e0) * 64) : 0;
       const int valid1 = ((e1 >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e1) * 64) : 0;
+      uint32_t colmask[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      if (masks != nullptr) {
+        const unsigned long long m0 = valid0 > 0 ? __ldg(masks + 2 * j) : 0ull;
+        const unsigned long long m1 = valid1 > 0 ? __ldg(masks + 2 * j + 1) : 0ull;
+        colmask[0] = uint32_t(m0); colmask[1] = uint32_t(m0 >> 32);
+        colmask[2] = uint32_t(m1); colmask[3] = uint32_t(m1 >> 32);
+      }
       ok = mbar_wait(bar(SB_S_FULL + t), j & 1, ab, p.err, 601);
       if (!ok) break;
       tc_fence_after();
       float mx0, mx1;
-      softmax_online_step<D, true>(s_addr, s_addr, o_addr, valid0, valid1, c, j == 0, st, mx0, mx1);
+      softmax_online_step<D, true>(s_addr, s_addr, o_addr, valid0, valid1, c, j == 0, st, mx0, mx1,
+                                   masks != nullptr ? colmask : nullptr);
       tc_fence_before();
       mbar_arrive(bar(SB_P_FULL + t));
     }

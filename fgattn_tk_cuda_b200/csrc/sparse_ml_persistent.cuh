@@ -54,6 +54,12 @@ struct SparseMLParams {
   int* queue;                // global item counter (zeroed before the launch)
   int* err;
   int* redo;                 // RENORM: [BH * npairs] flags (zeroed before the launch); 1 = item must be re-run
+  // Token-derived lists (null = key-block lists of 64-row query blocks): every 128-row query block has ONE
+  // list, [BH, npairs, list_stride] ascending key blocks, and kb_mask gives the live columns of each listed
+  // block ([BH, npairs, list_stride], bit j = key 64 * block + j takes part).  route (optional,
+  // [BH * npairs]): items with route == 0 are left to another kernel.
+  const unsigned long long* kb_mask;
+  const int* route;
   int S, S_pad, kv_len, nqb, nkb, npairs, n_items, list_stride, list_cap;
   float scale_log2;
   long long* stats;          // tuning builds (-DFG_STATS), debug & 8: per-CTA cycle counters [gridDim.x][32]
@@ -137,6 +143,25 @@ __device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[
     pk[i >> 1] = pack_bf16(p0, p1);
   }
 }
+// The same with an arbitrary set of live columns (bit i of `live` = column i takes part).
+template <bool SUM>
+__device__ __forceinline__ void ml_probs_masked(const uint32_t (&r)[32], uint32_t (&pk)[16], uint32_t live, float c,
+                                                float t_row, float& sum0, float& sum1) {
+  const uint64_t c2 = f2_pack(c, c), nt2 = f2_pack(-t_row, -t_row);
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float x0, x1;
+    f2_unpack(f2_fma(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, nt2), x0, x1);
+    float p0 = ex2(x0), p1 = ex2(x1);
+    if (!((live >> i) & 1u)) p0 = 0.f;
+    if (!((live >> (i + 1)) & 1u)) p1 = 0.f;
+    if (SUM) {
+      sum0 += p0;
+      sum1 += p1;
+    }
+    pk[i >> 1] = pack_bf16(p0, p1);
+  }
+}
 
 // Cycle accounting for tuning builds (-DFG_STATS); compiled out otherwise.
 #ifdef FG_STATS
@@ -147,7 +172,8 @@ __device__ __forceinline__ void ml_probs(const uint32_t (&r)[N], uint32_t (&pk)[
 #define FG_CLK() 0ll
 #endif
 
-template <int D, bool RENORM>
+// TOKEN: token-derived lists with column masks (SparseMLParams::kb_mask), otherwise key-block lists
+template <int D, bool RENORM, bool TOKEN = false>
 __global__ void __launch_bounds__(SparseMLCfg<D>::kThreads, 1)
 sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                             const __grid_constant__ CUtensorMap mv, const SparseMLParams p) {
@@ -223,9 +249,14 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       bool ok = true;
       if (it >= NLB) FG_TW(w_le, ok = mbar_wait_relaxed(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001));
       if (!ok) break;
-      int g = 0;
-      if (lane == 0) g = atomicAdd(p.queue, 1);
-      g = __shfl_sync(0xffffffffu, g, 0);
+      int g = 0, item = 0;
+      for (;;) {                                           // next item of the queue that is routed to this kernel
+        if (lane == 0) g = atomicAdd(p.queue, 1);
+        g = __shfl_sync(0xffffffffu, g, 0);
+        if (g >= p.n_items) break;
+        item = p.order[g];
+        if (!TOKEN || !p.route || p.route[item] != 0) break;
+      }
       if (g >= p.n_items) {
         if (lane == 0) {
           info[lb].n_steps = -1;
@@ -233,9 +264,10 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         }
         break;
       }
-      const int item = p.order[g];
       const int bh = item / p.npairs;
       const int pair = item - bh * p.npairs;
+      constexpr bool token_lists = TOKEN;
+      const int list_rows = token_lists ? p.npairs : p.nqb;
       for (int w = lane; w < 2 * words; w += 32) bm0[w] = 0u;
       __syncwarp();
       // both halves' counts are fetched before either list is walked
@@ -243,12 +275,12 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       const int* src_half[2];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int qb = pair * 2 + half;
+        const int qb = token_lists ? pair : pair * 2 + half;     // token lists: both halves walk the one list
         n_half[half] = 0;
         src_half[half] = p.kb_idx;
-        if (qb < p.nqb) {
-          src_half[half] = p.kb_idx + (size_t(bh) * p.nqb + qb) * p.list_stride;
-          n_half[half] = min(p.kb_cnt[size_t(bh) * p.nqb + qb], p.list_stride);
+        if (qb < list_rows) {
+          src_half[half] = p.kb_idx + (size_t(bh) * list_rows + qb) * p.list_stride;
+          n_half[half] = min(p.kb_cnt[size_t(bh) * list_rows + qb], p.list_stride);
         }
       }
 #pragma unroll
@@ -552,6 +584,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 #endif
         t_prol += FG_CLK() - tp0;
         const uint32_t* list = lists + lb * p.list_cap;
+        // token-derived lists: the union list is the block's own list, so entry i of it has column mask i
+        const unsigned long long* masks =
+            TOKEN ? p.kb_mask + (size_t(bh) * p.npairs + pair) * p.list_stride : nullptr;
         for (int j = 0; j < n; ++j, ++s) {
           if ((s & 1) != own) {
             // the other pair's step; an item's first step is a good moment for the pending rows
@@ -563,6 +598,8 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           }
           const uint32_t e = list[2 * j + kb_sel];
           const int valid_kb = ((e >> (30 + half)) & 1u) ? min(64, p.kv_len - entry_kb(e) * 64) : 0;
+          unsigned long long live64 = ~0ull;               // fetched before the wait for the scores
+          if (TOKEN && valid_kb > 0) live64 = __ldg(masks + 2 * j + kb_sel);
           const int sbuf = s % kSB;
           FG_TW(w_s, ok = mbar_wait(bar(PB_S_FULL + s % 6), (s / 6) & 1, ab, p.err, 1403));
           if (!ok) break;
@@ -576,11 +613,14 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           for (int ch = 0; ch < 2; ++ch) {
             const int valid = max(0, min(32, valid_kb - ch * 32));
             uint32_t pk[16];
-            if (valid > 0 && !(dbg & 4)) {               // warp-uniform
+            const uint32_t live =
+                TOKEN ? uint32_t(live64 >> (32 * ch)) & (valid >= 32 ? 0xffffffffu : ((1u << valid) - 1u)) : 0xffffffffu;
+            if (valid > 0 && live != 0u && !(dbg & 4)) {   // warp-uniform
               uint32_t r[32];
               tmem_ld32(a + ch * 32, r);
               tmem_ld_wait();
-              ml_probs<32, RENORM>(r, pk, valid, c, t_row, sum0, sum1);
+              if (!TOKEN || live == 0xffffffffu) ml_probs<32, RENORM>(r, pk, valid, c, t_row, sum0, sum1);
+              else ml_probs_masked<RENORM>(r, pk, live, c, t_row, sum0, sum1);
             } else {
 #pragma unroll
               for (int i = 0; i < 16; ++i) pk[i] = 0u;
@@ -657,7 +697,8 @@ sparse_order_kernel(const int* __restrict__ kb_cnt, int* __restrict__ order, int
   __shared__ int hist[kBuckets];
   __shared__ int part[256];
   const int tid = threadIdx.x;
-  const int u0 = blockIdx.x * group_heads, u1 = min(n_units, u0 + group_heads);
+  // the last group takes whatever is left (the launcher may make it larger than the others)
+  const int u0 = blockIdx.x * group_heads, u1 = (blockIdx.x == gridDim.x - 1) ? n_units : min(n_units, u0 + group_heads);
   const int n = (u1 - u0) * npairs;
   if (blockIdx.x == 0 && tid == 0) *queue = 0;
   if (redo)

@@ -22,6 +22,9 @@ struct TokenParams {
   // 128-row query blocks
   const int* order;
   int pairs;
+  // optional [BH, nqb]: query blocks with route != 0 are computed by the block-route kernel and are left
+  // alone here (no loads, no stores)
+  const int* route;
   float scale_log2;
 };
 
@@ -140,6 +143,15 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
   const int item = p.order ? p.order[blockIdx.x] : int(blockIdx.x);
   const int bh = item / p.pairs;
   const int q0 = (item - bh * p.pairs) * 256;
+  bool skip[2] = {false, false};
+  if (p.route) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int qb = (q0 >> 7) + t;
+      skip[t] = qb >= p.nqb || p.route[size_t(bh) * p.nqb + qb] != 0;
+    }
+    if (skip[0] && skip[1]) return;                      // CTA-uniform, before any set-up
+  }
 
   if (tid == 0) {
     ab->flag = 0;
@@ -173,7 +185,7 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
     const int qb = (q0 >> 7) + t;
     cnt[t] = 0;
     lst[t] = p.kv_idx;
-    if (qb < p.nqb) {
+    if (qb < p.nqb && !skip[t]) {
       cnt[t] = max(0, min(p.kv_cnt[size_t(bh) * p.nqb + qb], p.mask_stride));
       lst[t] = p.kv_idx + (size_t(bh) * p.nqb + qb) * p.mask_stride;
     }
@@ -341,7 +353,9 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
       fetch_live(j + 1);
     }
     __nv_bfloat16* orow = p.o + (size_t(bh) * p.S + row) * D;
-    if (nst[t] == 0) {
+    if (skip[t]) {
+      // another kernel owns these rows
+    } else if (nst[t] == 0) {
       if (row < p.S) {
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);

@@ -46,7 +46,9 @@ int fgattn_last_cuda_error(void);
  * reference.)  "group_heads": (batch, head) units per group of the longest-first thread-block orders
  * (0 = built-in choice, negative = back to the environment variable FGATTN_GROUP_HEADS, which is read
  * once per process); "dense_persist": 1 / 0 forces the persistent / one-item form of the dense family,
- * -1 = chosen by key length, below -1 = back to FGATTN_DENSE_PERSIST. */
+ * -1 = chosen by key length, below -1 = back to FGATTN_DENSE_PERSIST; "token_block_route": 1 allows the
+ * block route of fgattn_sp_attn (given the large workspace), 0 keeps it on the row gather (default),
+ * negative = back to FGATTN_TOKEN_BLOCK_ROUTE. */
 int fgattn_set_tuning(const char* name, int value);
 /* Synchronise `stream` and report whether any kernel launched through this library on the current
  * device gave up on a bounded wait.  Returns FGATTN_OK or FGATTN_DEVICE_TIMEOUT; *code (optional)
@@ -112,9 +114,17 @@ int fgattn_all_index_mask(int* kv_indices, int* kv_num_indices, int batch, int h
  * block, softmax restricted to the listed key tokens (renormalised), times the listed v rows.
  * kv_indices int32 [B,H,ceil(S/128),mask_stride], kv_num_indices int32 [B,H,ceil(S/128)].
  * Replaces attn_sparse_fwd_wg_impl (python/extension.cpp:10-14, python/cuda_attn.cu:41-75), the
- * sp_attn operator (python/extension.cpp:125-154).  `workspace` (fgattn_sp_attn_workspace_bytes, scratch)
- * is optional: with it the thread blocks take the query blocks longest list first, which shortens the
- * end of the launch when list lengths differ; null = storage order.  Same result either way. */
+ * sp_attn operator (python/extension.cpp:125-154).  `workspace` (scratch) is optional and comes in two
+ * sizes.  With fgattn_sp_attn_workspace_bytes the thread blocks take the query blocks longest list first,
+ * which shortens the end of the launch when list lengths differ; null = storage order.  With
+ * fgattn_sp_attn_token_workspace_bytes AND the "token_block_route" knob of fgattn_set_tuning switched on,
+ * the call additionally converts every list into the 64-key blocks it touches plus a column mask per
+ * block, and query blocks whose listed tokens fill at least three quarters of the touched blocks load
+ * those blocks whole by TMA instead of gathering rows (include/asyncloadutils.cuh:73-153) -- the unlisted
+ * columns are switched off in the softmax; lists that are scattered or name a token twice stay on the
+ * row gather.  It pays for lists made of (nearly) whole key blocks (1.24x at C3 with every token of the
+ * kept blocks listed); threshold-mask lists fill 55-60 % of the blocks they touch and are faster on the
+ * row gather, which is why the knob is off by default.  Same result within rounding in every case. */
 int fgattn_sp_attn(void* o, const void* q, const void* k, const void* v, const int* kv_indices,
                    const int* kv_num_indices, int mask_stride, int batch, int heads, int seq, int D, int kv_rows,
                    float scale, void* workspace, size_t workspace_bytes, void* stream);
@@ -183,6 +193,11 @@ int fgattn_sp_attn_blocks_ml(void* o, const void* q, const void* k, const void* 
  * processing order of the query-block pairs, re-run flags).  The workspace is scratch: contents need not
  * survive the call, but two calls that may overlap on the device must not share it. */
 size_t fgattn_sp_attn_workspace_bytes(int batch, int heads, int seq);
+
+/* Bytes of the large workspace that lets fgattn_sp_attn take the block route (see there): the two queue
+ * regions plus, per 128-row query block, the touched key blocks of its token list with their column
+ * masks (12 bytes per query block and key block), a route flag and a per-row exponent hint. */
+size_t fgattn_sp_attn_token_workspace_bytes(int batch, int heads, int seq, int kv_rows);
 
 /* fgattn_sp_attn_blocks (renormalising softmax over the kept key blocks, the sp_attn semantics of
  * include/sparseattn_asyncgatherload_padded.cuh:198-249) at the speed of fgattn_sp_attn_blocks_ml, for
