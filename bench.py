@@ -37,9 +37,9 @@ import torch  # noqa: E402
 
 METRIC = "sparse_fwd_tflops_on_kept_blocks"
 UNIT = "TFLOP/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_ml_persistent_kernel<128> launch over the
-# first 16 heads of C3 (one ncu capture); the traffic grows in proportion to the heads of a launch
-NCU_DRAM_BYTES_PER_C3_HEAD = 312.0e6 / 16.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one sparse_ml_persistent_kernel<128> launch over the 32
+# heads of C3 (one ncu capture of this command with --sections none: 761 MB read + 122 MB written)
+NCU_DRAM_BYTES_PER_C3_HEAD = 883.0e6 / 32.0
 
 
 def read_peaks():
@@ -679,7 +679,7 @@ def main():
                          "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
                          "frac_200_steps_of_sustained": F_sparse / ms_200 / 1e9 / peaks["bf16_tflops_sustained"],
                          "traffic": NCU_DRAM_BYTES_PER_C3_HEAD * B * H if args.workload == "c3" else None,
-                         "traffic_source": "one ncu capture of a 16-head launch, scaled by heads"},
+                         "traffic_source": "one ncu capture of the 32-head launch, per head x heads of this run"},
             "stages": stages, "strong": strong, "configs": configs,
         }
         if e2e:
