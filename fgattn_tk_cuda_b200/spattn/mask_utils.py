@@ -21,6 +21,22 @@ def _pad128(n: int) -> int:
     return 128 * ((n + 127) // 128)
 
 
+class nvtx_range:
+    """NVTX range around one stage of the path (max_q / denom + lists, token mask, compaction, sparse
+    attention, dense attention), so that a timeline shows the stages by name; the reference's profiling
+    recipe picks kernels by name instead (profile.sh:5).  Costs nothing measurable without a profiler."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
 # ------------------------------------------------------------------------------------------------
 # mask caches (python/spattn/mask_utils.py:17-98): decide on which diffusion runs the mask is
 # rebuilt and hand the cached lists to the sparse steps in between
@@ -162,7 +178,8 @@ def _maxq_denom(q, k):
     B, H, S, _ = q.shape
     max_q = torch.empty((B, H, 1, _pad128(S)), dtype=torch.float32, device=q.device)
     denom = torch.empty_like(max_q)
-    spattn_interface.maxq_denom(max_q, denom, q.contiguous(), k.contiguous())
+    with nvtx_range("fgattn.maxq_denom"):
+        spattn_interface.maxq_denom(max_q, denom, q.contiguous(), k.contiguous())
     return max_q, denom
 
 
@@ -171,8 +188,9 @@ def qk_bitmask_from_maxq_denom_cuda(max_q, denom, q, k, thresh, blocksz=128):
     assert blocksz == 128
     B, H, S, _ = q.shape
     mask = torch.empty((B, H, (S + 127) // 128, max_q.shape[3]), device=q.device, dtype=torch.int32)
-    spattn_interface.booleanmask_128(mask, max_q.contiguous(), denom.contiguous(), q.contiguous(), k.contiguous(),
-                                     thresh)
+    with nvtx_range("fgattn.token_mask"):
+        spattn_interface.booleanmask_128(mask, max_q.contiguous(), denom.contiguous(), q.contiguous(), k.contiguous(),
+                                         thresh)
     return mask
 
 
@@ -184,7 +202,9 @@ def qk_token_mask_cuda(q, k, thresh, v=None):
     kb_idx, kb_cnt, max_q, denom, *out = qk_block_indexmask_cuda(q, k, thresh, v=v)
     B, H, S, _ = q.shape
     mask = torch.empty((B, H, (S + 127) // 128, _pad128(k.shape[2])), device=q.device, dtype=torch.int32)
-    spattn_interface.booleanmask_128_listed(mask, max_q, denom, q.contiguous(), k.contiguous(), thresh, kb_idx, kb_cnt)
+    with nvtx_range("fgattn.token_mask_in_kept_blocks"):
+        spattn_interface.booleanmask_128_listed(mask, max_q, denom, q.contiguous(), k.contiguous(), thresh, kb_idx,
+                                                kb_cnt)
     return (mask, max_q, denom, *out)
 
 
@@ -200,8 +220,10 @@ def bitmask_to_indexmask_cuda(booleanmask, seq=None):
     B, H, SB, stride = booleanmask.shape
     kv_indices = torch.empty((B, H, SB, stride), device=booleanmask.device, dtype=torch.int32)
     num_kv_indices = torch.empty((B, H, SB), device=booleanmask.device, dtype=torch.int32)
-    spattn_interface.booleanmask_to_indexmask(kv_indices, num_kv_indices, booleanmask.to(torch.int32).contiguous(),
-                                              stride if seq is None else seq)
+    with nvtx_range("fgattn.mask_to_lists"):
+        spattn_interface.booleanmask_to_indexmask(kv_indices, num_kv_indices,
+                                                  booleanmask.to(torch.int32).contiguous(),
+                                                  stride if seq is None else seq)
     return kv_indices, num_kv_indices
 
 
@@ -251,8 +273,9 @@ def qk_block_indexmask_cuda(q, k, thresh, v=None):
     max_q = torch.empty((B, H, 1, _pad128(S)), dtype=torch.float32, device=q.device)
     denom = torch.empty_like(max_q)
     o = torch.empty((B, H, S, D), device=q.device, dtype=torch.bfloat16) if v is not None else None
-    spattn_interface.block_index_lists(kb_indices, kb_counts, max_q, denom, o, q.contiguous(), k.contiguous(),
-                                       None if v is None else v.contiguous(), thresh, _block_scratch(q, k))
+    with nvtx_range("fgattn.maxq_denom+block_lists" + ("+full_attn" if v is not None else "")):
+        spattn_interface.block_index_lists(kb_indices, kb_counts, max_q, denom, o, q.contiguous(), k.contiguous(),
+                                           None if v is None else v.contiguous(), thresh, _block_scratch(q, k))
     return (kb_indices, kb_counts, max_q, denom) + ((o,) if v is not None else ())
 
 

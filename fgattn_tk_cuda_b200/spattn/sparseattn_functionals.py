@@ -25,7 +25,8 @@ def _ml(query):
 def baseline_attn(query, key, value, current_layer=None, ditrun=None, *args, **kwargs):
     """Dense attention (sparseattn_functionals.py:10-15)."""
     out = _out(query)
-    spattn_interface.full_attn(out, query.contiguous(), key.contiguous(), value.contiguous())
+    with mask_utils.nvtx_range("fgattn.full_attn"):
+        spattn_interface.full_attn(out, query.contiguous(), key.contiguous(), value.contiguous())
     return out
 
 
@@ -33,7 +34,9 @@ def baseline_attn_maxq_denom(query, key, value, current_layer=None, ditrun=None,
     """Dense attention that also computes max_q / denom (sparseattn_functionals.py:18-26)."""
     out = _out(query)
     max_q, denom = _ml(query)
-    spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(), value.contiguous())
+    with mask_utils.nvtx_range("fgattn.full_attn+maxq_denom"):
+        spattn_interface.fullattn_maxq_denom(out, max_q, denom, query.contiguous(), key.contiguous(),
+                                             value.contiguous())
     return out
 
 
@@ -45,14 +48,16 @@ def _sparse(out, query, key, value, mask, blocksz=128):
     such a cached block mask together with the max_q of the run that built it, which the renormalising
     persistent kernel takes as its per-row exponent hint."""
     q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
-    if len(mask) == 4:
-        spattn_interface.sp_attn_blocks_ml(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2], mask[3])
-    elif len(mask) == 3:
-        spattn_interface.sp_attn_blocks_hint(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2])
-    elif blocksz == 64:
-        spattn_interface.sp_attn_blocks(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
-    else:
-        spattn_interface.sp_attn(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
+    with mask_utils.nvtx_range("fgattn.sparse_attention"):
+        if len(mask) == 4:
+            spattn_interface.sp_attn_blocks_ml(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2],
+                                               mask[3])
+        elif len(mask) == 3:
+            spattn_interface.sp_attn_blocks_hint(out, q, k, v, mask[0].contiguous(), mask[1].contiguous(), mask[2])
+        elif blocksz == 64:
+            spattn_interface.sp_attn_blocks(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
+        else:
+            spattn_interface.sp_attn(out, q, k, v, mask[0].contiguous(), mask[1].contiguous())
     return out
 
 
