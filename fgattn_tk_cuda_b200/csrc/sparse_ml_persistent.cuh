@@ -85,7 +85,12 @@ struct SparseMLCfg {
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = 2 * kTileBytes;
   static constexpr int kOffV = kOffK + kKStages * kTileBytes;
-  static constexpr int kOffBar = kOffV + kVStages * kTileBytes;
+  // D = 64 leaves 64 columns of tensor memory free next to the accumulator: the renormalising form keeps its
+  // row sums there, l = P * 1 as one more (N = 16) product per P*V step against a tile of ones, so the softmax
+  // threads add nothing up.  The tile of ones: 16 keys x 64 columns of bf16 1.0 (2 KiB, any layout).
+  static constexpr bool kTensorRowSum = (D == 64);
+  static constexpr int kOffOnes = kOffV + kVStages * kTileBytes;
+  static constexpr int kOffBar = kOffOnes + (kTensorRowSum ? 2048 : 0);
   static constexpr int kBarBytes = 768;
   // [kListBufs][list_cap] entries, then [2][words] bitmaps, then [4][4][128] partial row sums (RENORM)
   static constexpr int kOffList = kOffBar + kBarBytes;
@@ -200,6 +205,13 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
 #endif
   constexpr uint32_t kColS = 0, kColO = 384;           // three 128-column score buffers, then the accumulator
   constexpr int kSB = 3;
+  constexpr bool TSUM = RENORM && Cfg::kTensorRowSum;  // row sums by the tensor cores, 16 columns behind O
+  constexpr uint32_t kColL = kColO + 64;
+  if constexpr (TSUM) {
+    uint32_t* ones = reinterpret_cast<uint32_t*>(smem + Cfg::kOffOnes);
+    for (int i = tid; i < 512; i += Cfg::kThreads) ones[i] = 0x3F803F80u;     // bf16 1.0 pairs
+    fence_proxy_async_smem();
+  }
 
   if (tid == 0) {
     ab->flag = 0;
@@ -444,6 +456,8 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     // ------------------------------------------------------------------ P V issuer
     reg_dealloc<Cfg::kRegsService>();
     const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
+    const uint32_t idesc_l = umma_idesc_bf16(128, 16, true);
+    const uint64_t ones_desc = umma_smem_desc_sw128(sbase + Cfg::kOffOnes, 16384, 1024);
     int s = 0, u = 0;
     bool ok = true;
     long long w_v = 0, w_p = 0, w_o = 0, w_misc = 0, t_start = FG_CLK();
@@ -473,6 +487,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
                 const int ks = kb * 4 + kk;                   // 16-key step inside the 128-key tile
                 umma_ts_elect(tmem + kColO, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8,
                               umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                if constexpr (TSUM)                          // l += P * 1
+                  umma_ts_elect(tmem + kColL, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8, ones_desc, idesc_l,
+                                (j > 0 || ks > 0) ? 1u : 0u);
               }
             }
           }
@@ -516,11 +533,22 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       if (!ok) return;
       float inv = 1.0f;
       if constexpr (RENORM) {
-        // the four warpgroups' partial sums of this row; the row's output is O / l
-        FG_TW(w_epi, ok = mbar_wait(bar(PB_L_FULL + (pe_u & 3)), (pe_u >> 2) & 1, ab, p.err, 1404));
-        if (!ok) return;
-        const float* ls = rowsum + (pe_u & 3) * (Cfg::kSmWGs * 128) + row_in_tile;
-        const float l = (ls[0] + ls[128]) + (ls[256] + ls[384]);
+        float l;
+        if constexpr (TSUM) {
+          // the row sum sits in tensor memory next to the accumulator (every one of its 16 columns)
+          tc_fence_after();
+          uint32_t lv[16];
+          tmem_ld16(lane_base + kColL, lv);
+          tmem_ld_wait();
+          l = __uint_as_float(lv[0]);
+        } else {
+          // the four warpgroups' partial sums of this row
+          FG_TW(w_epi, ok = mbar_wait(bar(PB_L_FULL + (pe_u & 3)), (pe_u >> 2) & 1, ab, p.err, 1404));
+          if (!ok) return;
+          const float* ls = rowsum + (pe_u & 3) * (Cfg::kSmWGs * 128) + row_in_tile;
+          l = (ls[0] + ls[128]) + (ls[256] + ls[384]);
+        }
+        // the row's output is O / l
         const bool good = (l >= 0x1p-60f) && (l <= 0x1p100f);        // false for NaN, too
         inv = good ? 1.0f / l : 0.f;
         if (pe_in && pe_listed && !good) p.redo[pe_item] = 1;
@@ -619,8 +647,8 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
               uint32_t r[32];
               tmem_ld32(a + ch * 32, r);
               tmem_ld_wait();
-              if (!TOKEN || live == 0xffffffffu) ml_probs<32, RENORM>(r, pk, valid, c, t_row, sum0, sum1);
-              else ml_probs_masked<RENORM>(r, pk, live, c, t_row, sum0, sum1);
+              if (!TOKEN || live == 0xffffffffu) ml_probs<32, RENORM && !TSUM>(r, pk, valid, c, t_row, sum0, sum1);
+              else ml_probs_masked<RENORM && !TSUM>(r, pk, live, c, t_row, sum0, sum1);
             } else {
 #pragma unroll
               for (int i = 0; i < 16; ++i) pk[i] = 0u;
@@ -643,11 +671,13 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         if (pe) epilogue();                              // (only when the loop above did not run it)
         if (!ok) break;
         if constexpr (RENORM) {
-          // A buffer of four items: a warpgroup can be at most three steps (so three items) ahead of the
-          // P*V issuer, which starts the item after next only once every warp has read this one's sums.
-          rowsum[(u & 3) * (Cfg::kSmWGs * 128) + wg * 128 + row_in_tile] = sum0 + sum1;
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(PB_L_FULL + (u & 3)));
+          if constexpr (!TSUM) {
+            // A buffer of four items: a warpgroup can be at most three steps (so three items) ahead of the
+            // P*V issuer, which starts the item after next only once every warp has read this one's sums.
+            rowsum[(u & 3) * (Cfg::kSmWGs * 128) + wg * 128 + row_in_tile] = sum0 + sum1;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(PB_L_FULL + (u & 3)));
+          }
           pe_u = u;
           pe_item = bh * p.npairs + pair;
           pe_listed = (halves >> half) & 1;
