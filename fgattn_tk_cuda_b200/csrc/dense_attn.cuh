@@ -34,6 +34,11 @@ struct DenseParams {
   int S, S_pad, kv_len, n_kv_tiles, nkb, mask_stride;
   int bh0;              // first (batch*head) unit of this launch (blockmax is relative to it)
   int n_pairs, n_items; // query tile pairs per unit; work items of this launch (units * n_pairs)
+  // One-item form only: thread blocks [0, half_from) take one item each; the items from half_from on are cut
+  // in two and thread block half_from + 2i + t takes query tile t of item half_from + i alone.  The launcher
+  // cuts the items of the last, partial wave when both halves of all of them fit on the SMs at once: a
+  // half item takes about half the time, so the wave ends early instead of leaving most SMs idle.
+  int half_from;
   // kTokenMask, optional: key-block lists of the 64-row query blocks ([BH, nqb64, list_stride], counts
   // [BH, nqb64]); a CTA then visits only the 128-key tiles that some list of its four query blocks names
   const int* kb_idx;
@@ -89,8 +94,14 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   AbortState* ab = reinterpret_cast<AbortState*>(smem + Cfg::kOffBar + 8 * BAR_COUNT + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int first_item = (MODE == kTokenMask && p.order) ? p.order[blockIdx.x] : int(blockIdx.x);
+  int first_item = (MODE == kTokenMask && p.order) ? p.order[blockIdx.x] : int(blockIdx.x);
   const int item_step = gridDim.x;
+  uint32_t tiles = 3u;                 // bit t: query tile t of the item is computed by this thread block
+  if (!PERSIST && MODE != kTokenMask && int(blockIdx.x) >= p.half_from) {
+    const int h = int(blockIdx.x) - p.half_from;
+    first_item = p.half_from + (h >> 1);
+    tiles = 1u << (h & 1);
+  }
 
   if (tid == 0) {
     ab->flag = 0;
@@ -254,6 +265,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           if (ok) {
             tc_fence_after();
             for (int t = 0; t < 2; ++t) {
+              if (!((tiles >> t) & 1u)) continue;
               issue_qk(t, g0 % Cfg::kKStages, t * 128);
               umma_commit_elect(bar(BAR_S_FULL + t * 2));
             }
@@ -268,6 +280,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             const int ks = (g + 1) % Cfg::kKStages;
             if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((g + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
             for (int t = 0; t < 2 && ok; ++t) {
+              if (!((tiles >> t) & 1u)) continue;
               ok = mbar_wait_warp(bar(BAR_P_FULL + t), g & 1, ab, p.err, 205);
               if (!ok) break;
               tc_fence_after();
@@ -293,6 +306,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             const uint32_t f = g >> 1;
             ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (g / Cfg::kKStages) & 1, ab, p.err, 206);
             for (int t = 0; t < 2 && ok; ++t) {
+              if (!((tiles >> t) & 1u)) continue;
               if (f > 0) ok = mbar_wait_warp(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
               if (!ok) break;
               tc_fence_after();
@@ -316,7 +330,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     const int row_in_tile = wq * 32 + lane;
     const uint32_t lane_base = tmem + (uint32_t(wq * 32) << 16);
     const float c = p.scale_log2;
-    bool ok = true;
+    bool ok = ((tiles >> t) & 1u) != 0;                // a half item: the other tile's warpgroup has nothing to do
     uint32_t g0 = 0;                                   // K/V tiles of the items before this one
     int it = 0;
     for (int item = first_item; item < p.n_items && ok; item += item_step, ++it, g0 += n_tiles) {
@@ -394,6 +408,14 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
       // ---- epilogue of the item
+      if (ok && HAS_V) {
+        ok = mbar_wait(bar(BAR_O_FULL + t), it & 1, ab, p.err, 302);
+        if (ok) {
+          tc_fence_after();
+          store_o_row<D>(lane_base + 256 + t * 128, p.o + (size_t(p.bh0 + bh) * p.S + row) * D, 1.0f / st.l, row < p.S);
+          tc_fence_before();       // the next item's first P V product overwrites O(t)
+        }
+      }
       if (ok && WRITE_ML) {
         if (row < p.S) {
           p.max_q[ml_off] = st.m_true;
@@ -401,14 +423,6 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         } else if (row < p.S_pad) {
           p.max_q[ml_off] = 0.f;
           p.denom[ml_off] = -INFINITY;
-        }
-      }
-      if (ok && HAS_V) {
-        ok = mbar_wait(bar(BAR_O_FULL + t), it & 1, ab, p.err, 302);
-        if (ok) {
-          tc_fence_after();
-          store_o_row<D>(lane_base + 256 + t * 128, p.o + (size_t(p.bh0 + bh) * p.S + row) * D, 1.0f / st.l, row < p.S);
-          tc_fence_before();       // the next item's first P V product overwrites O(t)
         }
       }
       if (!PERSIST) break;

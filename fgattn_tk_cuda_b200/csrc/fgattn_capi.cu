@@ -69,7 +69,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // the persistent / one-item form of the dense family; -1 = by key length).
 // fgattn_set_tuning overrides either for the rest of the process.
 constexpr int kTuningUnset = -2147483647 - 1;
-std::atomic<int> g_tune_group_heads{kTuningUnset}, g_tune_dense_persist{kTuningUnset}, g_tune_token_route{kTuningUnset};
+std::atomic<int> g_tune_group_heads{kTuningUnset}, g_tune_dense_persist{kTuningUnset}, g_tune_token_route{kTuningUnset},
+    g_tune_dense_halves{kTuningUnset};
 int env_group_heads() {
   const int t = g_tune_group_heads.load(std::memory_order_relaxed);
   if (t != kTuningUnset) return t;
@@ -83,6 +84,13 @@ bool env_token_block_route() {
   const int t = g_tune_token_route.load(std::memory_order_relaxed);
   if (t != kTuningUnset) return t != 0;
   static const int v = [] { const char* e = getenv("FGATTN_TOKEN_BLOCK_ROUTE"); return e ? atoi(e) : 0; }();
+  return v != 0;
+}
+// "dense_halves" (FGATTN_DENSE_HALVES): 0 = never cut the last wave's items in two
+bool env_dense_halves() {
+  const int t = g_tune_dense_halves.load(std::memory_order_relaxed);
+  if (t != kTuningUnset) return t != 0;
+  static const int v = [] { const char* e = getenv("FGATTN_DENSE_HALVES"); return e ? atoi(e) : 1; }();
   return v != 0;
 }
 int env_dense_persist() {
@@ -161,7 +169,21 @@ int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
       return launch_dense_k<D, MODE, BLOCKMAX, true>(mq, mk, mv, pp, pp.n_items < sms ? pp.n_items : sms, st);
     }
   }
-  return launch_dense_k<D, MODE, BLOCKMAX, false>(mq, mk, mv, pp, pp.n_items, st);
+  // One thread block per item.  When the last wave of thread blocks would be less than half full, its items
+  // are cut into their two query tiles (DenseParams::half_from), so that the wave takes about half as long.
+  int ctas = pp.n_items;
+  pp.half_from = pp.n_items;
+  if constexpr (MODE != fg::kTokenMask) {
+    int sms = 0;
+    int r = sm_count(&sms);
+    if (r) return r;
+    const int rest = pp.n_items % sms;
+    if (rest > 0 && 2 * rest <= sms && env_dense_halves()) {
+      pp.half_from = pp.n_items - rest;
+      ctas = pp.half_from + 2 * rest;
+    }
+  }
+  return launch_dense_k<D, MODE, BLOCKMAX, false>(mq, mk, mv, pp, ctas, st);
 }
 
 template <int MODE, bool BLOCKMAX>
@@ -305,6 +327,7 @@ int fgattn_set_tuning(const char* name, int value) {
   if (!strcmp(name, "group_heads")) g_tune_group_heads.store(value < 0 ? kTuningUnset : value);
   else if (!strcmp(name, "dense_persist")) g_tune_dense_persist.store(value < -1 ? kTuningUnset : value);
   else if (!strcmp(name, "token_block_route")) g_tune_token_route.store(value < 0 ? kTuningUnset : value);
+  else if (!strcmp(name, "dense_halves")) g_tune_dense_halves.store(value < 0 ? kTuningUnset : value);
   else return FGATTN_INVALID_ARGUMENT;
   return FGATTN_OK;
 }

@@ -311,6 +311,35 @@ __device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 2^x for a pair of values on the FMA pipe instead of the MUFU: x = n + f with n = round(x) taken from the
+// low mantissa bits of x + 1.5 * 2^23, f in [-0.5, 0.5], a cubic minimax polynomial for 2^f (relative error
+// below 1e-4, far under the resolution of the bf16 probabilities it feeds) and n added into the exponent
+// field.  Inputs are clamped at -126 (results below 2^-126 do not matter to a softmax).
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  const uint64_t x = f2_pack(x0, x1);
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);            // 1.5 * 2^23
+  const uint64_t xr = f2_add(x, magic);                                // integer part in the low mantissa bits
+  const uint64_t xi = f2_add(xr, f2_pack(-12582912.0f, -12582912.0f));
+  const uint64_t f = f2_fma(xi, f2_pack(-1.0f, -1.0f), x);
+  uint64_t q = f2_fma(f, f2_pack(0.05517160892486572f, 0.05517160892486572f),
+                      f2_pack(0.2426111102104187f, 0.2426111102104187f));
+  q = f2_fma(q, f, f2_pack(0.6932609677314758f, 0.6932609677314758f));
+  q = f2_fma(q, f, f2_pack(0.9999280571937561f, 0.9999280571937561f));
+  float q0, q1, r0, r1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(xr, r0, r1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -28,7 +28,12 @@ __device__ __forceinline__ void online_init(OnlineState& st) {
 //   o_addr : the row's D fp32 output accumulator columns (rescaled in place when the maximum grows)
 // Returns the raw maxima of the two 64-key halves through mx0 / mx1.
 //   colmask: optional 128-bit column mask (4 words, bit set = live column) applied on top
-template <int D, bool WRITE_P>
+//   POLY   : of every eight pairs of columns, how many compute their exponentials on the FMA pipe
+//            (ex2_poly2) instead of the MUFU, which is the busiest unit of these kernels.  Measured with
+//            L2 flushed between calls: 2 of 8 with P*V (C2 0.245 -> 0.232 ms, C4 5.33 -> 5.11 ms, C3 within
+//            2 %), 3 of 8 for the max / denominator pass (C3 2.49 -> 2.38 ms, C4 3.94 -> 3.45 ms); 4 of 8 is
+//            slower again: the polynomial costs ten issue slots per pair against two
+template <int D, bool WRITE_P, int POLY = (WRITE_P ? 2 : 3)>
 __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, int valid0,
                                                     int valid1, float c, bool first, OnlineState& st, float& mx0,
                                                     float& mx1, const uint32_t* colmask = nullptr) {
@@ -105,8 +110,23 @@ __device__ __forceinline__ void softmax_online_step(uint32_t s_addr, uint32_t p_
     }
 #pragma unroll
     for (int i = w * 32; i < w * 32 + 32; i += 2) {
-      const float p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
-      const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+      float p0, p1;
+      if constexpr (POLY > 0) {
+        // packed scale-and-shift; the pairs that take the FMA-pipe exponential are spread evenly
+        const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), f2_pack(c, c),
+                                   f2_pack(neg_m, neg_m));
+        if ((((i >> 1) & 7) * POLY) % 8 < POLY) {
+          ex2_poly2(x2, p0, p1);
+        } else {
+          float x0, x1;
+          f2_unpack(x2, x0, x1);
+          p0 = ex2(x0);
+          p1 = ex2(x1);
+        }
+      } else {
+        p0 = ex2(fmaf(__uint_as_float(r[i]), c, neg_m));
+        p1 = ex2(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+      }
       sum0 += p0;
       sum1 += p1;
       if (WRITE_P) r[i >> 1] = pack_bf16(p0, p1);

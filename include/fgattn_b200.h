@@ -46,7 +46,9 @@ int fgattn_last_cuda_error(void);
  * reference.)  "group_heads": (batch, head) units per group of the longest-first thread-block orders
  * (0 = built-in choice, negative = back to the environment variable FGATTN_GROUP_HEADS, which is read
  * once per process); "dense_persist": 1 / 0 forces the persistent / one-item form of the dense family,
- * -1 = chosen by key length, below -1 = back to FGATTN_DENSE_PERSIST; "token_block_route": 1 allows the
+ * -1 = chosen by key length, below -1 = back to FGATTN_DENSE_PERSIST; "dense_halves": 0 keeps the dense family from cutting the items of a
+ * less-than-half-full last wave of thread blocks into their two query tiles (1 = default, negative = back
+ * to FGATTN_DENSE_HALVES); "token_block_route": 1 allows the
  * block route of fgattn_sp_attn (given the large workspace), 0 keeps it on the row gather (default),
  * negative = back to FGATTN_TOKEN_BLOCK_ROUTE. */
 int fgattn_set_tuning(const char* name, int value);
