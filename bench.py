@@ -358,8 +358,24 @@ def main():
     u_over = union_overhead(idx, cnt, nkb)
     scratch = spattn.mask_utils._block_scratch(q)
 
+    # ---- the timed region first (nothing but the set-up has run on the GPU before it): exactly K steps after
+    # W warm-up steps, barrier + synchronize on both sides
+    step = lambda: ops.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ms_step, clocks = timed_region(step, args.steps, gpu_index)
+    barrier()
+    capi.check()
+    # the same step 200 times back to back (power cap territory), and a 20-step burst, each with its clock
+    ms_200, clocks_200 = timed_region(step, 200, gpu_index)
+    time.sleep(0.5)
+    for _ in range(3):
+        step()
+    ms_burst, clocks_burst = timed_region(step, 20, gpu_index)
     stages = {}
     if "stages" in sections:
+        time.sleep(0.5)
         ms_full = ev_time(lambda: capi.full_attn(o, q, k, v), 5, 2)
         ms_lists = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch), 5, 2)
         ms_maxq = ev_time(lambda: capi.maxq_denom(max_q, denom, q, k), 5, 2)
@@ -434,20 +450,6 @@ def main():
         # re-build the lists that the stage timings overwrote with equal content (same inputs)
         capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch)
 
-    # ---- the timed region: exactly K steps after W warm-up steps, barrier + synchronize on both sides
-    step = lambda: ops.sp_attn_blocks_ml(o, q, k, v, idx, cnt, max_q, denom)  # noqa: E731
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    ms_step, clocks = timed_region(step, args.steps, gpu_index)
-    barrier()
-    capi.check()
-    # the same step 200 times back to back (power cap territory), and a 20-step burst, each with its clock
-    ms_200, clocks_200 = timed_region(step, 200, gpu_index)
-    time.sleep(0.5)
-    for _ in range(3):
-        step()
-    ms_burst, clocks_burst = timed_region(step, 20, gpu_index)
     if stages:
         stages.update({"sparse_ms": ms_step, "sparse_speedup_over_full": stages["full_attn_ms"] / ms_step,
                        "ideal_speedup_1_over_density": 1.0 / density,
@@ -607,10 +609,14 @@ def main():
         c2 = synth.WORKLOADS["c2"]
         q2, k2, v2 = synth.make_qkv(c2, device=dev)
         o2 = torch.empty_like(q2)
+        torch.cuda.synchronize()
+        time.sleep(1.0)                      # the sections before ran the GPU into its power cap
+        sampler = ClockSampler(gpu_index)
+        sampler.start()
         ms = ev_time(lambda: capi.full_attn(o2, q2, k2, v2), 10, 3, flush=flush)
         F2 = 4.0 * c2.B * c2.H * c2.S * c2.S * c2.D
         configs["c2_dense"] = {"workload": c2.name, "full_attn_ms": ms, "full_attn_tflops": F2 / ms / 1e9,
-                               "full_attn_frac_of_peak": F2 / ms / 1e9 / peak,
+                               "full_attn_frac_of_peak": F2 / ms / 1e9 / peak, "clocks": sampler.stop(),
                                "l2": "64 MiB of q,k,v,o: a 256 MiB buffer is written before every timed call"}
         del q2, k2, v2, o2
         c4 = synth.WORKLOADS["c4"]
@@ -622,6 +628,10 @@ def main():
         sc4 = spattn.mask_utils._block_scratch(q4)
         F4 = 4.0 * c4.B * c4.H * c4.S * c4.S * c4.D
         Fs4 = 4.0 * 64 * 64 * c4.D * nnz4
+        torch.cuda.synchronize()
+        time.sleep(1.0)
+        sampler = ClockSampler(gpu_index)
+        sampler.start()
         ms_f = ev_time(lambda: capi.full_attn(o4, q4, k4, v4), 5, 2)
         ms_l = ev_time(lambda: capi.block_index_lists(i4, n4, m4, l4, q4, k4, c4.tau, sc4), 5, 2)
         ms_s = ev_time(lambda: ops.sp_attn_blocks_ml(o4, q4, k4, v4, i4, n4, m4, l4), 20, 3)
@@ -636,7 +646,7 @@ def main():
                                 "sparse_renorm_ms": ms_r, "sparse_renorm_tflops_on_kept_blocks": Fs4 / ms_r / 1e9,
                                 "sparse_hint_ms": ms_h, "sparse_hint_tflops_on_kept_blocks": Fs4 / ms_h / 1e9,
                                 "sparse_speedup_over_full": ms_f / ms_s, "speedup_gap": (1.0 / d4) / (ms_f / ms_s),
-                                "union_overhead": union_overhead(i4, n4, nb4)}
+                                "union_overhead": union_overhead(i4, n4, nb4), "clocks": sampler.stop()}
         capi.check()
         del q4, k4, v4, o4, flush
     barrier()
