@@ -238,19 +238,26 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
       auto issue_qk = [&](int t, int kstage, uint32_t d_col) {
         const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffK + kstage * Cfg::kTileBytes;
+        // one election per product: a lane elected per instruction makes the issue itself the limit
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_ss_elect(tmem + d_col, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
-                  idesc_qk, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+            umma_ss(tmem + d_col, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                    idesc_qk, ks > 0);
+          }
         }
+        __syncwarp();
       };
       auto issue_pv = [&](int t, int vstage, bool acc) {
         const uint32_t va = sbase + Cfg::kOffV + vstage * Cfg::kTileBytes;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)   // 128 keys, 16 per UMMA
-          umma_ts_elect(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
-                  idesc_pv, (acc || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks)   // 128 keys, 16 per UMMA
+            umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+                    idesc_pv, (acc || ks > 0) ? 1u : 0u);
+        }
+        __syncwarp();
       };
       bool ok = true;
       uint32_t g0 = 0;                      // K/V tiles of the items before this one

@@ -220,18 +220,11 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Issue from a converged warp: one elected lane executes the instruction.  Keeping the surrounding
-// loop warp-uniform lets the compiler hold descriptors in uniform registers, which halves the issue
-// cost of tcgen05.mma compared with a loop that runs under `if (lane == 0)`.
-__device__ __forceinline__ void umma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                              uint32_t accumulate) {
-  if (elect_one()) umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
-}
-__device__ __forceinline__ void umma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                              uint32_t accumulate) {
-  if (elect_one()) umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
-}
-
+// Issue pattern: the issuing warp stays converged, elects one lane ONCE per product (`if (elect_one()) { all
+// the product's tcgen05.mma and its commits } __syncwarp();`) and keeps the surrounding loop warp-uniform.
+// Electing a lane for every single instruction makes the issue itself the limit as soon as a product has more
+// than four shared-memory-operand instructions: measured 115 clocks per 128x128x16 UMMA against the 64 clocks
+// the tensor pipe needs (the D = 128 score product then takes 918 clocks instead of 513).
 // mbarrier arrives once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

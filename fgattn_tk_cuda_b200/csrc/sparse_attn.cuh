@@ -251,14 +251,17 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
         if (!ok) return;
         tc_fence_after();
         const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+        if (elect_one()) {             // one election for the product and its commits
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_ss_elect(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
-                  idesc_qk, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+            umma_ss(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                    idesc_qk, ks > 0);
+          }
+          umma_commit(bar(SB_S_FULL + t));
+          umma_commit(bar(SB_EMPTY + st));
         }
-        umma_commit_elect(bar(SB_S_FULL + t));
-        umma_commit_elect(bar(SB_EMPTY + st));
+        __syncwarp();
         ++idx;
       };
       auto pv = [&](int t, int j) {
@@ -268,11 +271,14 @@ sparse_block_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_co
         if (!ok) return;
         tc_fence_after();
         const uint32_t va = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts_elect(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
-                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit_elect(bar(SB_EMPTY + st));
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+                    idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(bar(SB_EMPTY + st));
+        }
+        __syncwarp();
         ++idx;
       };
       if (ok && n0 > 0) qk(0);

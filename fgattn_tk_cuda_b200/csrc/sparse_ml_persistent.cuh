@@ -433,17 +433,22 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           if (!ok) break;
           tc_fence_after();
           const uint32_t ka = sbase + Cfg::kOffK + ks * Cfg::kTileBytes;
-          if (!(dbg & 2)) {
+          // One election for the whole product and its commits: electing a lane per instruction makes
+          // the issue itself the limit (about 115 clocks per UMMA against the 64 the tensor pipe needs).
+          if (elect_one()) {
+            if (!(dbg & 2)) {
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-              umma_ss_elect(tmem + kColS + sbuf * 128, umma_smem_desc_sw128(qa + off, 16, 1024),
-                            umma_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0);
+              for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+                umma_ss(tmem + kColS + sbuf * 128, umma_smem_desc_sw128(qa + off, 16, 1024),
+                        umma_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0);
+              }
             }
+            umma_commit(bar(PB_S_FULL + s % 6));
+            umma_commit(bar(PB_K_EMPTY + ks));
+            if (j == n - 1) umma_commit(bar(PB_Q_EMPTY + qb));
           }
-          umma_commit_elect(bar(PB_S_FULL + s % 6));
-          umma_commit_elect(bar(PB_K_EMPTY + ks));
-          if (j == n - 1) umma_commit_elect(bar(PB_Q_EMPTY + qb));
+          __syncwarp();
         }
         ++u;
       }
@@ -482,21 +487,27 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
             if (!ok) break;
             tc_fence_after();
             if (!(dbg & 2)) {
+              if (elect_one()) {
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                const int ks = kb * 4 + kk;                   // 16-key step inside the 128-key tile
-                umma_ts_elect(tmem + kColO, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8,
-                              umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                if constexpr (TSUM)                          // l += P * 1
-                  umma_ts_elect(tmem + kColL, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8, ones_desc, idesc_l,
-                                (j > 0 || ks > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 4; ++kk) {
+                  const int ks = kb * 4 + kk;                   // 16-key step inside the 128-key tile
+                  umma_ts(tmem + kColO, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8,
+                          umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                  if constexpr (TSUM)                          // l += P * 1
+                    umma_ts(tmem + kColL, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8, ones_desc, idesc_l,
+                            (j > 0 || ks > 0) ? 1u : 0u);
+                }
               }
+              __syncwarp();
             }
           }
           if (!ok) break;
-          umma_commit_elect(bar(PB_V_EMPTY + vs));
-          umma_commit_elect(bar(PB_S_EMPTY + pbuf));       // scores and probabilities of this buffer are consumed
-          if (j == n - 1) umma_commit_elect(bar(PB_O_FULL));
+          if (elect_one()) {
+            umma_commit(bar(PB_V_EMPTY + vs));
+            umma_commit(bar(PB_S_EMPTY + pbuf));           // scores and probabilities of this buffer are consumed
+            if (j == n - 1) umma_commit(bar(PB_O_FULL));
+          }
+          __syncwarp();
         }
         ++u;
       }

@@ -283,14 +283,17 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
         if (!ok) return;
         tc_fence_after();
         const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+        if (elect_one()) {             // one election for the product and its commits
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_ss_elect(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
-                  idesc_qk, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+            umma_ss(tmem + t * 128, umma_smem_desc_sw128(qa + off, 16, 1024), umma_smem_desc_sw128(ka + off, 16, 1024),
+                    idesc_qk, ks > 0);
+          }
+          umma_commit(bar(TB_S_FULL + t));
+          umma_commit(bar(TB_EMPTY + st));
         }
-        umma_commit_elect(bar(TB_S_FULL + t));
-        umma_commit_elect(bar(TB_EMPTY + st));
+        __syncwarp();
         ++idx;
       };
       auto pv = [&](int t, int j) {
@@ -300,11 +303,14 @@ sparse_token_attn_kernel(const __grid_constant__ CUtensorMap mq, const TokenPara
         if (!ok) return;
         tc_fence_after();
         const uint32_t va = sbase + Cfg::kOffRing + st * Cfg::kTileBytes;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts_elect(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
-                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit_elect(bar(TB_EMPTY + st));
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, umma_smem_desc_sw128(va + ks * 2048, 16384, 1024),
+                    idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(bar(TB_EMPTY + st));
+        }
+        __syncwarp();
         ++idx;
       };
       if (ok && nst[0] > 0) qk(0);

@@ -117,17 +117,20 @@ topk_scores_kernel(const __grid_constant__ CUtensorMap m_hi, const __grid_consta
     if (ok) {
       tc_fence_after();
       const uint32_t idesc = umma_idesc_bf16(128, 128, false);
+      if (elect_one()) {               // one election for both products and the commit
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        const uint32_t a = part ? a_lo : a_hi;
+        for (int part = 0; part < 2; ++part) {
+          const uint32_t a = part ? a_lo : a_hi;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss_elect(tmem, umma_smem_desc_sw128(a + off, 16, 1024), umma_smem_desc_sw128(b_k + off, 16, 1024), idesc,
-                        (part | kk) ? 1u : 0u);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+            umma_ss(tmem, umma_smem_desc_sw128(a + off, 16, 1024), umma_smem_desc_sw128(b_k + off, 16, 1024), idesc,
+                    (part | kk) ? 1u : 0u);
+          }
         }
+        umma_commit(bar_done);
       }
-      umma_commit_elect(bar_done);
+      __syncwarp();
     }
   } else {
     // epilogue: one query-block row per thread -> shared-memory tile (16-byte chunks XOR-swizzled by
