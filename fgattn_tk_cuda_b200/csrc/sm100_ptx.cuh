@@ -346,3 +346,12 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
 }
 
 }  // namespace fg
+
+// Cycle accounting for tuning builds (-DFG_STATS); compiled out otherwise.
+#ifdef FG_STATS
+#define FG_TW(acc, expr) do { long long t__ = clock64(); expr; acc += clock64() - t__; } while (0)
+#define FG_CLK() clock64()
+#else
+#define FG_TW(acc, expr) do { expr; } while (0)
+#define FG_CLK() 0ll
+#endif

@@ -168,14 +168,6 @@ __device__ __forceinline__ void ml_probs_masked(const uint32_t (&r)[32], uint32_
   }
 }
 
-// Cycle accounting for tuning builds (-DFG_STATS); compiled out otherwise.
-#ifdef FG_STATS
-#define FG_TW(acc, expr) do { long long t__ = clock64(); expr; acc += clock64() - t__; } while (0)
-#define FG_CLK() clock64()
-#else
-#define FG_TW(acc, expr) do { expr; } while (0)
-#define FG_CLK() 0ll
-#endif
 
 // TOKEN: token-derived lists with column masks (SparseMLParams::kb_mask), otherwise key-block lists
 template <int D, bool RENORM, bool TOKEN = false>
