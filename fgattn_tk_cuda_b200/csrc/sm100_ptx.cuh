@@ -3,6 +3,7 @@
 // Every wait on an mbarrier is bounded: when the cycle budget runs out the waiter records an
 // error code and returns false, and the kernel tears down normally.
 #pragma once
+#include <cstdio>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -90,10 +91,18 @@ __device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, 
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
-      if (ab->flag) return false;
+      if (ab->flag) {
+#ifdef FG_WAIT_REPORT
+        if ((threadIdx.x & 31) == 0) printf("block %d warp %d: gave up in wait %d (parity %u) after another waiter's time-out\n", blockIdx.x, threadIdx.x >> 5, code, parity);
+#endif
+        return false;
+      }
       if (clock64() - t0 > budget) {
         ab->flag = 1;
         if (err) atomicCAS(err, 0, code);
+#ifdef FG_WAIT_REPORT
+        if ((threadIdx.x & 31) == 0) printf("block %d warp %d: time-out in wait %d (parity %u)\n", blockIdx.x, threadIdx.x >> 5, code, parity);
+#endif
         return false;
       }
     }
