@@ -238,7 +238,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
       auto issue_qk = [&](int t, int kstage, uint32_t d_col) {
         const uint32_t qa = sbase + Cfg::kOffQ + t * Cfg::kTileBytes, ka = sbase + Cfg::kOffK + kstage * Cfg::kTileBytes;
-        // one election per product: a lane elected per instruction makes the issue itself the limit
+        // one election per product (see the note on issue in sm100_ptx.cuh)
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {

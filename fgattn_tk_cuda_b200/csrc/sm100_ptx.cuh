@@ -232,8 +232,9 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 // Issue pattern: the issuing warp stays converged, elects one lane ONCE per product (`if (elect_one()) { all
 // the product's tcgen05.mma and its commits } __syncwarp();`) and keeps the surrounding loop warp-uniform.
 // Electing a lane for every single instruction makes the issue itself the limit as soon as a product has more
-// than four shared-memory-operand instructions: measured 115 clocks per 128x128x16 UMMA against the 64 clocks
-// the tensor pipe needs (the D = 128 score product then takes 918 clocks instead of 513).
+// than four shared-memory-operand instructions: measured, with products issued back to back, 115 clocks per
+// 128x128x16 UMMA against the 64 clocks the tensor pipe needs (the D = 128 score product then takes 918 clocks
+// instead of 513; inside the attention kernels, where other things bound a step, the difference is 0-7 %).
 // mbarrier arrives once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

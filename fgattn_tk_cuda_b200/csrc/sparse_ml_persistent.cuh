@@ -425,8 +425,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           if (!ok) break;
           tc_fence_after();
           const uint32_t ka = sbase + Cfg::kOffK + ks * Cfg::kTileBytes;
-          // One election for the whole product and its commits: electing a lane per instruction makes
-          // the issue itself the limit (about 115 clocks per UMMA against the 64 the tensor pipe needs).
+          // one election for the whole product and its commits (see the note on issue in sm100_ptx.cuh)
           if (elect_one()) {
             if (!(dbg & 2)) {
 #pragma unroll
