@@ -72,7 +72,11 @@ struct SparseMLCfg {
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kKStages = (D == 128) ? 2 : 4;
   static constexpr int kVStages = (D == 128) ? 2 : 4;
-  static constexpr int kListBufs = 4;
+  // Items the scheduler may be ahead of the slowest reader of a list.  Measured: at D = 128 two is better than
+  // four (C3 0.622 -> 0.604 ms, 32 units of the C5 shape 7.62 -> 7.34 ms; three lies in between), at D = 64 four is
+  // better than two (C4 0.401 -> 0.432 ms): its items are short and a step takes 1000 instead of 1650 clocks, so
+  // the lists have to be under way earlier.
+  static constexpr int kListBufs = (D == 128) ? 2 : 4;
   // warp roles: [0, kSmWarps) softmax, then K producer, QK issuer, scheduler, PV issuer, V producer
   static constexpr int kSmWGs = 4;                        // two pairs of softmax warpgroups
   static constexpr int kSmWarps = 4 * kSmWGs;
