@@ -12,7 +12,8 @@
 // producer fetches the next item's Q and first K/V tiles while the last steps of the current one are
 // still being computed, and tensor memory is allocated once per CTA.  Warp roles:
 //   warps 0-3  softmax of query tile 0 (one row per thread)      warp 8  TMA producer
-//   warps 4-7  softmax of query tile 1                            warp 9  UMMA issuer
+//   warps 4-7  softmax of query tile 1                            warps 9, 10  UMMA issuers (with V at D = 128
+//                                                                  one per query tile, else warp 9 alone)
 // S = Q K^T accumulates in tensor memory; the softmax warps read it with tcgen05.ld, write the
 // bf16 probabilities back over the same columns and the PV product takes them from tensor memory.
 #pragma once
@@ -85,6 +86,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   using Cfg = DenseCfg<D>;
   constexpr bool HAS_V = (MODE == kFull || MODE == kFullML);
   constexpr bool WRITE_ML = (MODE == kFullML || MODE == kML);
+  constexpr bool TWO_ISS = HAS_V && D == 128;            // one UMMA issuer warp per query tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -105,13 +107,15 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 
   if (tid == 0) {
     ab->flag = 0;
+    // with two issuer warps (one per query tile) a K / V stage (or Q) is free when both have let go
+    const int n_iss = TWO_ISS ? __popc(tiles) : 1;
     mbar_init(bar(BAR_Q_FULL), 1);
-    mbar_init(bar(BAR_Q_EMPTY), 1);
+    mbar_init(bar(BAR_Q_EMPTY), n_iss);
     for (int s = 0; s < 4; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
-      mbar_init(bar(BAR_K_EMPTY + s), 1);
+      mbar_init(bar(BAR_K_EMPTY + s), n_iss);
       mbar_init(bar(BAR_V_FULL + s), 1);
-      mbar_init(bar(BAR_V_EMPTY + s), 1);
+      mbar_init(bar(BAR_V_EMPTY + s), n_iss);
       mbar_init(bar(BAR_S_FULL + s), 1);
       mbar_init(bar(BAR_S_EMPTY + s), 128);
     }
@@ -230,10 +234,15 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ UMMA issuer
+  } else if (warp == 9 || (TWO_ISS && warp == 10)) {
+    // ------------------------------------------------------------------ UMMA issuers
+    // With V at D = 128 one warp per query tile: a tile's steps form a chain (scores, softmax, P V and next
+    // scores), and an issuer that serves both tiles in turn reaches a tile's probabilities late whenever it is
+    // busy with the other tile's waits and commits (C3 3.38 -> 3.20 ms).  Otherwise one warp serves both tiles
+    // (at D = 64 the softmax, not the chain, bounds a step, and two issuers are 1 % slower).
     reg_dealloc<72>();
-    {   // whole warp, uniform control flow; single instructions go through an elected lane
+    const int t_lo = TWO_ISS ? warp - 9 : 0, t_hi = TWO_ISS ? t_lo + 1 : 2;
+    if (!TWO_ISS || ((tiles >> t_lo) & 1u)) {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
       auto issue_qk = [&](int t, int kstage, uint32_t d_col) {
@@ -271,7 +280,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           if (ok) ok = mbar_wait_warp(bar(BAR_K_FULL + g0 % Cfg::kKStages), (g0 / Cfg::kKStages) & 1, ab, p.err, 202);
           if (ok) {
             tc_fence_after();
-            for (int t = 0; t < 2; ++t) {
+            for (int t = t_lo; t < t_hi; ++t) {
               if (!((tiles >> t) & 1u)) continue;
               issue_qk(t, g0 % Cfg::kKStages, t * 128);
               umma_commit_elect(bar(BAR_S_FULL + t * 2));
@@ -286,7 +295,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             const bool more = (j + 1 < n_tiles);
             const int ks = (g + 1) % Cfg::kKStages;
             if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((g + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
-            for (int t = 0; t < 2 && ok; ++t) {
+            for (int t = t_lo; t < t_hi && ok; ++t) {
               if (!((tiles >> t) & 1u)) continue;
               ok = mbar_wait_warp(bar(BAR_P_FULL + t), g & 1, ab, p.err, 205);
               if (!ok) break;
@@ -312,7 +321,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             const int ks = g % Cfg::kKStages, b = g & 1;
             const uint32_t f = g >> 1;
             ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (g / Cfg::kKStages) & 1, ab, p.err, 206);
-            for (int t = 0; t < 2 && ok; ++t) {
+            for (int t = t_lo; t < t_hi && ok; ++t) {
               if (!((tiles >> t) & 1u)) continue;
               if (f > 0) ok = mbar_wait_warp(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
               if (!ok) break;
