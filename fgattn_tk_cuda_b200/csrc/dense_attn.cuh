@@ -12,8 +12,9 @@
 // producer fetches the next item's Q and first K/V tiles while the last steps of the current one are
 // still being computed, and tensor memory is allocated once per CTA.  Warp roles:
 //   warps 0-3  softmax of query tile 0 (one row per thread)      warp 8  TMA producer
-//   warps 4-7  softmax of query tile 1                            warps 9, 10  UMMA issuers (with V at D = 128
-//                                                                  one per query tile, else warp 9 alone)
+//   warps 4-7  softmax of query tile 1                            warps 9, 10  UMMA issuers (one per query tile;
+//                                                                  with V at D = 64 and in the token-mask
+//                                                                  mode warp 9 alone)
 // S = Q K^T accumulates in tensor memory; the softmax warps read it with tcgen05.ld, write the
 // bf16 probabilities back over the same columns and the PV product takes them from tensor memory.
 #pragma once
@@ -86,7 +87,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   using Cfg = DenseCfg<D>;
   constexpr bool HAS_V = (MODE == kFull || MODE == kFullML);
   constexpr bool WRITE_ML = (MODE == kFullML || MODE == kML);
-  constexpr bool TWO_ISS = HAS_V && D == 128;            // one UMMA issuer warp per query tile
+  constexpr bool TWO_ISS = (HAS_V && D == 128) || MODE == kML;   // one UMMA issuer warp per query tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -238,8 +239,10 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // ------------------------------------------------------------------ UMMA issuers
     // With V at D = 128 one warp per query tile: a tile's steps form a chain (scores, softmax, P V and next
     // scores), and an issuer that serves both tiles in turn reaches a tile's probabilities late whenever it is
-    // busy with the other tile's waits and commits (C3 3.38 -> 3.20 ms).  Otherwise one warp serves both tiles
-    // (at D = 64 the softmax, not the chain, bounds a step, and two issuers are 1 % slower).
+    // busy with the other tile's waits and commits (C3 3.38 -> 3.20 ms).  The max / denominator mode gains the
+    // same way (a freed score buffer is refilled at once: C3 2.32 -> 2.18 ms, C4 3.43 -> 3.36 ms).  With V at
+    // D = 64 the softmax, not the chain, bounds a step, two issuers are 1 % slower there and one warp serves
+    // both tiles, as in the token-mask mode.
     reg_dealloc<72>();
     const int t_lo = TWO_ISS ? warp - 9 : 0, t_hi = TWO_ISS ? t_lo + 1 : 2;
     if (!TWO_ISS || ((tiles >> t_lo) & 1u)) {   // whole warp, uniform control flow; single instructions go through an elected lane
