@@ -87,6 +87,9 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   using Cfg = DenseCfg<D>;
   constexpr bool HAS_V = (MODE == kFull || MODE == kFullML);
   constexpr bool WRITE_ML = (MODE == kFullML || MODE == kML);
+  // without V the V ring's shared memory (it follows the K ring) holds K tiles as well
+  constexpr int kKSt = HAS_V ? Cfg::kKStages : Cfg::kKStages + Cfg::kVStages;
+  static_assert(kKSt <= 4, "barrier slots");
   constexpr bool TWO_ISS = (HAS_V && D == 128) || MODE == kML;   // one UMMA issuer warp per query tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -204,7 +207,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             tma_load_3d(sbase + Cfg::kOffQ + t * Cfg::kTileBytes + h * 16384, &mq, bar(BAR_Q_FULL), h * 64,
                         q0 + t * 128, p.bh0 + bh);
         for (int j = 0; j < n_tiles && ok; ++j, ++g) {
-          const int ks = g % Cfg::kKStages, kf = g / Cfg::kKStages;
+          const int ks = g % kKSt, kf = g / kKSt;
           if (kf > 0) ok = mbar_wait(bar(BAR_K_EMPTY + ks), (kf - 1) & 1, ab, p.err, 101);
           if (!ok) break;
           mbar_arrive_expect_tx(bar(BAR_K_FULL + ks), Cfg::kTileBytes);
@@ -227,10 +230,10 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         // let copies that are still in flight land before the CTA goes away: the last request to
         // every stage (a V request exists for tile x iff its K request does, except possibly the last)
         if (it > 0) mbar_wait_brief(bar(BAR_Q_FULL), (it - 1) & 1);
-        for (uint32_t s = 0; s < uint32_t(Cfg::kKStages); ++s) {
+        for (uint32_t s = 0; s < uint32_t(kKSt); ++s) {
           if (g <= s) continue;
-          const uint32_t last = ((g - 1 - s) / Cfg::kKStages) * Cfg::kKStages + s;   // last tile <= g-1 on stage s
-          mbar_wait_brief(bar(BAR_K_FULL + s), (last / Cfg::kKStages) & 1);
+          const uint32_t last = ((g - 1 - s) / kKSt) * kKSt + s;   // last tile <= g-1 on stage s
+          mbar_wait_brief(bar(BAR_K_FULL + s), (last / kKSt) & 1);
           if (HAS_V) mbar_wait_brief(bar(BAR_V_FULL + s), (last / Cfg::kVStages) & 1);
         }
       }
@@ -280,15 +283,15 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           // P(t) lives over S(t) and the tensor pipe runs in order, so the first product of an item may
           // follow the last P V of the previous one at once; O(t) is overwritten by the P V of step 0,
           // which waits for a P that the softmax warps write only after they have read the old O(t).
-          if (ok) ok = mbar_wait_warp(bar(BAR_K_FULL + g0 % Cfg::kKStages), (g0 / Cfg::kKStages) & 1, ab, p.err, 202);
+          if (ok) ok = mbar_wait_warp(bar(BAR_K_FULL + g0 % kKSt), (g0 / kKSt) & 1, ab, p.err, 202);
           if (ok) {
             tc_fence_after();
             for (int t = t_lo; t < t_hi; ++t) {
               if (!((tiles >> t) & 1u)) continue;
-              issue_qk(t, g0 % Cfg::kKStages, t * 128);
+              issue_qk(t, g0 % kKSt, t * 128);
               umma_commit_elect(bar(BAR_S_FULL + t * 2));
             }
-            umma_commit_elect(bar(BAR_K_EMPTY + g0 % Cfg::kKStages));
+            umma_commit_elect(bar(BAR_K_EMPTY + g0 % kKSt));
             if (n_tiles == 1) umma_commit_elect(bar(BAR_Q_EMPTY));
           }
           for (int j = 0; j < n_tiles && ok; ++j) {
@@ -296,8 +299,8 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             const int vs = g % Cfg::kVStages;
             ok = mbar_wait_warp(bar(BAR_V_FULL + vs), (g / Cfg::kVStages) & 1, ab, p.err, 203);
             const bool more = (j + 1 < n_tiles);
-            const int ks = (g + 1) % Cfg::kKStages;
-            if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((g + 1) / Cfg::kKStages) & 1, ab, p.err, 204);
+            const int ks = (g + 1) % kKSt;
+            if (ok && more) ok = mbar_wait_warp(bar(BAR_K_FULL + ks), ((g + 1) / kKSt) & 1, ab, p.err, 204);
             for (int t = t_lo; t < t_hi && ok; ++t) {
               if (!((tiles >> t) & 1u)) continue;
               ok = mbar_wait_warp(bar(BAR_P_FULL + t), g & 1, ab, p.err, 205);
@@ -321,9 +324,9 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           // no V: S is double-buffered per query tile; tile t, buffer b lives at column (2t+b)*128
           for (int j = 0; j < n_tiles && ok; ++j) {
             const uint32_t g = g0 + j;
-            const int ks = g % Cfg::kKStages, b = g & 1;
+            const int ks = g % kKSt, b = g & 1;
             const uint32_t f = g >> 1;
-            ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (g / Cfg::kKStages) & 1, ab, p.err, 206);
+            ok = mbar_wait_warp(bar(BAR_K_FULL + ks), (g / kKSt) & 1, ab, p.err, 206);
             for (int t = t_lo; t < t_hi && ok; ++t) {
               if (!((tiles >> t) & 1u)) continue;
               if (f > 0) ok = mbar_wait_warp(bar(BAR_S_EMPTY + t * 2 + b), (f - 1) & 1, ab, p.err, 207);
