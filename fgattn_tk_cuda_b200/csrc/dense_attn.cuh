@@ -90,7 +90,10 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   // without V the V ring's shared memory (it follows the K ring) holds K tiles as well
   constexpr int kKSt = HAS_V ? Cfg::kKStages : Cfg::kKStages + Cfg::kVStages;
   static_assert(kKSt <= 4, "barrier slots");
-  constexpr bool TWO_ISS = (HAS_V && D == 128) || MODE == kML;   // one UMMA issuer warp per query tile
+  constexpr bool TWO_ISS = (HAS_V && D == 128) || MODE == kML;   // one UMMA issuer warp per query tile ...
+  constexpr int kTwoIssMinTiles = 64;                            // ... from 8192 keys on: with fewer the second
+                                                                 // issuer's share of the item's start and end costs more
+                                                                 // than it gains (32768 x 1536 keys: +6 %, x 4096: +2 %)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -112,7 +115,7 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   if (tid == 0) {
     ab->flag = 0;
     // with two issuer warps (one per query tile) a K / V stage (or Q) is free when both have let go
-    const int n_iss = TWO_ISS ? __popc(tiles) : 1;
+    const int n_iss = (TWO_ISS && p.n_kv_tiles >= kTwoIssMinTiles) ? __popc(tiles) : 1;
     mbar_init(bar(BAR_Q_FULL), 1);
     mbar_init(bar(BAR_Q_EMPTY), n_iss);
     for (int s = 0; s < 4; ++s) {
@@ -238,17 +241,20 @@ dense_attn_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
     }
-  } else if (warp == 9 || (TWO_ISS && warp == 10)) {
+  } else if (warp == 9 || (TWO_ISS && warp == 10 && p.n_kv_tiles >= kTwoIssMinTiles)) {
     // ------------------------------------------------------------------ UMMA issuers
     // With V at D = 128 one warp per query tile: a tile's steps form a chain (scores, softmax, P V and next
     // scores), and an issuer that serves both tiles in turn reaches a tile's probabilities late whenever it is
     // busy with the other tile's waits and commits (C3 3.38 -> 3.20 ms).  The max / denominator mode gains the
     // same way (a freed score buffer is refilled at once: C3 2.32 -> 2.18 ms, C4 3.43 -> 3.36 ms).  With V at
     // D = 64 the softmax, not the chain, bounds a step, two issuers are 1 % slower there and one warp serves
-    // both tiles, as in the token-mask mode.
+    // both tiles, as in the token-mask mode and for key sequences under 8192.  (The gain depends on the data: on
+    // i.i.d. normal inputs, where no quarter of a score tile is ever skipped and the softmax step is longer, two
+    // issuers are level with one at 8192 keys and 1 % behind at 16384.)
     reg_dealloc<72>();
-    const int t_lo = TWO_ISS ? warp - 9 : 0, t_hi = TWO_ISS ? t_lo + 1 : 2;
-    if (!TWO_ISS || ((tiles >> t_lo) & 1u)) {   // whole warp, uniform control flow; single instructions go through an elected lane
+    const bool two_iss = TWO_ISS && p.n_kv_tiles >= kTwoIssMinTiles;
+    const int t_lo = two_iss ? warp - 9 : 0, t_hi = two_iss ? t_lo + 1 : 2;
+    if (!two_iss || ((tiles >> t_lo) & 1u)) {   // whole warp, uniform control flow; single instructions go through an elected lane
       const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
       const uint32_t idesc_pv = umma_idesc_bf16(128, D, true);
       auto issue_qk = [&](int t, int kstage, uint32_t d_col) {
