@@ -135,7 +135,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
   }
 }
 
-// Whole-warp variant for warp-uniform control flow (the UMMA issuer): every lane polls, the verdict
+// Whole-warp variant for warp-uniform control flow (the UMMA issuer): every lane polls, the outcome
 // is made uniform so that a following elect.sync sees a converged warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, AbortState* ab, int* err, int code) {
   const bool ok = mbar_wait(bar, parity, ab, err, code);
