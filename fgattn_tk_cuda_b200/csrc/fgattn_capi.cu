@@ -13,6 +13,7 @@
 #include "packed_mask.cuh"
 #include "selftest.cuh"
 #include "sparse_attn.cuh"
+#include "maxq_pass.cuh"
 #include "sparse_ml_persistent.cuh"
 #include "sparse_token_attn.cuh"
 #include "tensor_map.h"
@@ -70,7 +71,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // fgattn_set_tuning overrides either for the rest of the process.
 constexpr int kTuningUnset = -2147483647 - 1;
 std::atomic<int> g_tune_group_heads{kTuningUnset}, g_tune_dense_persist{kTuningUnset}, g_tune_token_route{kTuningUnset},
-    g_tune_dense_halves{kTuningUnset};
+    g_tune_dense_halves{kTuningUnset}, g_tune_maxq_wide{kTuningUnset};
 int env_group_heads() {
   const int t = g_tune_group_heads.load(std::memory_order_relaxed);
   if (t != kTuningUnset) return t;
@@ -92,6 +93,14 @@ bool env_dense_halves() {
   if (t != kTuningUnset) return t != 0;
   static const int v = [] { const char* e = getenv("FGATTN_DENSE_HALVES"); return e ? atoi(e) : 1; }();
   return v != 0;
+}
+// "maxq_wide" (FGATTN_MAXQ_WIDE): 0 sends the max / denominator pass through mode kML of the dense family
+// instead of the two-threads-per-row kernel (maxq_pass.cuh) where its one-item form runs; -1 / 1 = the default
+int env_maxq_wide() {
+  const int t = g_tune_maxq_wide.load(std::memory_order_relaxed);
+  if (t != kTuningUnset) return t;
+  static const int v = [] { const char* e = getenv("FGATTN_MAXQ_WIDE"); return e ? atoi(e) : -1; }();
+  return v;
 }
 int env_dense_persist() {
   const int t = g_tune_dense_persist.load(std::memory_order_relaxed);
@@ -153,6 +162,18 @@ int launch_dense_k(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 
 constexpr int kPersistMaxKeyTiles = 8;     // persistent CTAs up to 1024 keys
 
+// The max / denominator pass with two threads per row (maxq_pass.cuh); same parameters and grid as the
+// one-item form of the dense family.
+template <int D, bool BLOCKMAX>
+int launch_maxq_wide(const CUtensorMap& mq, const CUtensorMap& mk, const fg::DenseParams& p, int ctas, cudaStream_t st) {
+  auto kern = fg::maxq_pass_kernel<D, BLOCKMAX>;
+  int r = set_smem(kern, fg::MaxqCfg<D>::kSmemBytes);
+  if (r) return r;
+  kern<<<dim3(ctas, 1, 1), fg::MaxqCfg<D>::kThreads, fg::MaxqCfg<D>::kSmemBytes, st>>>(mq, mk, p);
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
 template <int D, int MODE, bool BLOCKMAX>
 int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const fg::DenseParams& p,
                    int nbh, cudaStream_t st) {
@@ -182,6 +203,11 @@ int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
       pp.half_from = pp.n_items - rest;
       ctas = pp.half_from + 2 * rest;
     }
+  }
+  if constexpr (MODE == fg::kML) {
+    const int wide_env = env_maxq_wide();
+    if (wide_env != 0)                     // faster at every key length of the one-item form (1536 keys and up)
+      return launch_maxq_wide<D, BLOCKMAX>(mq, mk, pp, ctas, st);
   }
   return launch_dense_k<D, MODE, BLOCKMAX, false>(mq, mk, mv, pp, ctas, st);
 }
@@ -328,6 +354,7 @@ int fgattn_set_tuning(const char* name, int value) {
   else if (!strcmp(name, "dense_persist")) g_tune_dense_persist.store(value < -1 ? kTuningUnset : value);
   else if (!strcmp(name, "token_block_route")) g_tune_token_route.store(value < 0 ? kTuningUnset : value);
   else if (!strcmp(name, "dense_halves")) g_tune_dense_halves.store(value < 0 ? kTuningUnset : value);
+  else if (!strcmp(name, "maxq_wide")) g_tune_maxq_wide.store(value < -1 ? kTuningUnset : value);
   else return FGATTN_INVALID_ARGUMENT;
   return FGATTN_OK;
 }

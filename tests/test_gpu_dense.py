@@ -111,3 +111,44 @@ def test_argument_errors():
     assert e.value.status == 1
     with pytest.raises(capi.FgattnError):
         capi.full_attn(torch.empty_like(q), q.float(), q, q)
+
+
+@pytest.mark.parametrize("B,H,S,D,kv", [(1, 2, 1500, 128, None),      # ragged last tile, 28 keys in its second half
+                                       (1, 2, 1664, 64, 1590),       # last tile's second half has no live key
+                                       (1, 30, 1280, 128, None),     # 150 items: the last wave's two are cut in halves
+                                       (2, 1, 2304, 64, 2111)])
+def test_maxq_two_threads_per_row(B, H, S, D, kv):
+    """Above 1024 keys maxq_denom runs the kernel that shares a row between two threads (one per 64-key block
+    of a score tile, partial (m, l) merged at the end); "maxq_wide" = 0 sends it through the dense family.
+    Both against the oracle, maxima identical, and the key-block lists built on either are the same."""
+    from oracle import fgattn_oracle as orc
+    capi = _capi()
+    g = torch.Generator().manual_seed(S + D)
+    q = torch.randn(B, H, S, D, generator=g)
+    k = torch.randn(B, H, S, D, generator=g) * torch.linspace(0.3, 2.5, S)[None, None, :, None]   # maxima keep growing
+    q, k = q.to(torch.bfloat16), k.to(torch.bfloat16)
+    qc, kc = q.cuda(), k.cuda()
+    rm, rl = orc.maxq_denom(q[:, :4], k[:, :4], kv_seq_len=kv)
+    nqb = nkb = (S + 63) // 64
+    out = {}
+    try:
+        for wide in (1, 0):
+            capi.set_tuning("maxq_wide", wide)
+            m, l = _ml_buffers(B, H, S)
+            capi.maxq_denom(m, l, qc, kc, kv_seq_len=kv)
+            capi.check()
+            _check_ml(m[:, :4], l[:, :4], rm[:, :, 0, :S], rl[:, :, 0, :S], S)
+            idx = torch.empty(B, H, nqb, nkb, dtype=torch.int32, device="cuda")
+            cnt = torch.empty(B, H, nqb, dtype=torch.int32, device="cuda")
+            m2, l2 = _ml_buffers(B, H, S)
+            scratch = torch.empty(capi.block_scratch_bytes(B, H, S) // 4, device="cuda")
+            capi.block_index_lists(idx, cnt, m2, l2, qc, kc, 1e-3, scratch, kv_seq_len=kv)
+            capi.check()
+            assert torch.equal(m2, m)
+            out[wide] = (m.cpu(), l.cpu(), idx.cpu(), cnt.cpu())
+    finally:
+        capi.set_tuning("maxq_wide", -1)
+    assert torch.equal(out[0][0], out[1][0])
+    np.testing.assert_allclose(out[0][1][..., :S].numpy(), out[1][1][..., :S].numpy(), rtol=5e-4)   # approximate exponentials, different summation order
+    # a block whose probability lies within 1e-3 of the threshold may flip with the summation order of l
+    assert (out[0][3] != out[1][3]).float().mean().item() <= 0.01
