@@ -94,8 +94,9 @@ bool env_dense_halves() {
   static const int v = [] { const char* e = getenv("FGATTN_DENSE_HALVES"); return e ? atoi(e) : 1; }();
   return v != 0;
 }
-// "maxq_wide" (FGATTN_MAXQ_WIDE): 0 sends the max / denominator pass through mode kML of the dense family
-// instead of the two-threads-per-row kernel (maxq_pass.cuh) where its one-item form runs; -1 / 1 = the default
+// "maxq_wide" (FGATTN_MAXQ_WIDE): 0 sends the max / denominator pass and the token mask over all key tiles
+// through modes kML / kTokenMask of the dense family instead of the two-threads-per-row kernel (maxq_pass.cuh)
+// where their one-item form runs; -1 / 1 = the default
 int env_maxq_wide() {
   const int t = g_tune_maxq_wide.load(std::memory_order_relaxed);
   if (t != kTuningUnset) return t;
@@ -164,9 +165,9 @@ constexpr int kPersistMaxKeyTiles = 8;     // persistent CTAs up to 1024 keys
 
 // The max / denominator pass with two threads per row (maxq_pass.cuh); same parameters and grid as the
 // one-item form of the dense family.
-template <int D, bool BLOCKMAX>
+template <int D, bool BLOCKMAX, bool TOKENMASK>
 int launch_maxq_wide(const CUtensorMap& mq, const CUtensorMap& mk, const fg::DenseParams& p, int ctas, cudaStream_t st) {
-  auto kern = fg::maxq_pass_kernel<D, BLOCKMAX>;
+  auto kern = fg::maxq_pass_kernel<D, BLOCKMAX, TOKENMASK>;
   int r = set_smem(kern, fg::MaxqCfg<D>::kSmemBytes);
   if (r) return r;
   kern<<<dim3(ctas, 1, 1), fg::MaxqCfg<D>::kThreads, fg::MaxqCfg<D>::kSmemBytes, st>>>(mq, mk, p);
@@ -204,10 +205,12 @@ int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
       ctas = pp.half_from + 2 * rest;
     }
   }
-  if constexpr (MODE == fg::kML) {
+  if constexpr (MODE == fg::kML || MODE == fg::kTokenMask) {
     const int wide_env = env_maxq_wide();
-    if (wide_env != 0)                     // faster at every key length of the one-item form (1536 keys and up)
-      return launch_maxq_wide<D, BLOCKMAX>(mq, mk, pp, ctas, st);
+    // faster at every key length of the one-item form (1536 keys and up); the token mask on listed tiles, whose
+    // items are a few tiles long, stays in the dense family
+    if (wide_env != 0 && !(MODE == fg::kTokenMask && p.kb_idx != nullptr))
+      return launch_maxq_wide<D, BLOCKMAX, MODE == fg::kTokenMask>(mq, mk, pp, ctas, st);
   }
   return launch_dense_k<D, MODE, BLOCKMAX, false>(mq, mk, mv, pp, ctas, st);
 }

@@ -19,6 +19,13 @@
 //   warps 0-3 / 4-7    softmax of query tile 0, keys 0-63 / 64-127 of every tile    warp 16      TMA producer
 //   warps 8-11 / 12-15 softmax of query tile 1                                      warps 17, 18 UMMA issuers
 // Tensor memory: the scores of each query tile are double-buffered (4 x 128 columns).
+//
+// TOKENMASK = true is the other pass of the dense family without V on the same skeleton: with (m, l) given, the
+// 128-row x 1-token threshold mask over all key tiles (mode kTokenMask of dense_attn.cuh, same parameters and
+// results).  A thread has no state there at all, so the column split is free: 32 heads of 16384 keys at D = 128
+// 1.69 -> 1.41 ms, 96 heads of 12345 keys at D = 64 2.02 -> 1.48 ms.  The form that visits only the key tiles named
+// by key-block lists stays in the dense family: its items are a few tiles long, and there the wider thread block
+// and the second issuer cost what the split gains (0.49 against 0.48-0.55 ms, 0.59 against 0.62 ms).
 #pragma once
 #include "dense_attn.cuh"
 #include "sm100_ptx.cuh"
@@ -115,7 +122,7 @@ __device__ __forceinline__ void maxq_step64(uint32_t s_addr, int valid, float c,
   st.l += sum0 + sum1;
 }
 
-template <int D, bool BLOCKMAX>
+template <int D, bool BLOCKMAX, bool TOKENMASK = false>
 __global__ void __launch_bounds__(MaxqCfg<D>::kThreads, 1)
 maxq_pass_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk, const DenseParams p) {
   using Cfg = MaxqCfg<D>;
@@ -131,12 +138,11 @@ maxq_pass_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int item = int(blockIdx.x);
   uint32_t tiles = 3u;                 // bit t: query tile t of the item is computed by this thread block
-  if (int(blockIdx.x) >= p.half_from) {
+  if (!TOKENMASK && int(blockIdx.x) >= p.half_from) {
     const int h = int(blockIdx.x) - p.half_from;
     item = p.half_from + (h >> 1);
     tiles = 1u << (h & 1);
   }
-  const int n_tiles = p.n_kv_tiles;
   const int bh = item / p.n_pairs, q0 = (item - bh * p.n_pairs) * 256;
 
   if (tid == 0) {
@@ -160,6 +166,7 @@ maxq_pass_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int n_tiles = p.n_kv_tiles;
 
   if (warp == Cfg::kWarpProd) {
     // ------------------------------------------------------------------ TMA producer
@@ -179,8 +186,8 @@ maxq_pass_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__
         if (!ok) break;
         mbar_arrive_expect_tx(bar(MQ_K_FULL + ks), Cfg::kTileBytes);
         for (int h = 0; h < Cfg::kHalves; ++h)
-          tma_load_3d(sbase + Cfg::kOffK + ks * Cfg::kTileBytes + h * 16384, &mk, bar(MQ_K_FULL + ks), h * 64, g * 128,
-                      p.bh0 + bh);
+          tma_load_3d(sbase + Cfg::kOffK + ks * Cfg::kTileBytes + h * 16384, &mk, bar(MQ_K_FULL + ks), h * 64,
+                      g * 128, p.bh0 + bh);
       }
       if (!ok) {
         // let the copies that are still in flight land before the thread block goes away
@@ -227,7 +234,51 @@ maxq_pass_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__
     const bool active = ((tiles >> t) & 1u) != 0;
     const int row = q0 + t * 128 + row_in_tile;            // query row in the sequence
     const size_t ml_off = size_t(p.bh0 + bh) * p.S_pad + row;
-    if (active) {
+    if constexpr (TOKENMASK) {
+      // keep bit of a token: some row of the 128-row block has s c - (m c + log2 l) > log2 tau, i.e. s > thr.
+      // Most 32-column quarters hold no such entry in any row of the warp: their row maxima settle that with one
+      // instruction per entry, and only the others build bits.
+      float thr = INFINITY;                                // rows past the sequence keep nothing
+      if (row < p.S) {
+        const float t_row = p.max_q[ml_off] * c + log2f(p.denom[ml_off]);      // the same expression as in the dense family
+        thr = (p.log2_tau + t_row) / c;
+      }
+      const bool block_in = q0 + t * 128 < p.S;
+      int* mrow0 = p.tokenmask + (size_t(p.bh0 + bh) * ((p.S + 127) >> 7) + ((q0 + t * 128) >> 7)) * p.mask_stride;
+      bool ok = true;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int b = j & 1;
+        ok = mbar_wait(bar(MQ_S_FULL + t * 2 + b), (j >> 1) & 1, ab, p.err, 623);
+        if (!ok) break;
+        tc_fence_after();
+        const int key0 = j * 128 + h * 64;               // first key of this thread's 64 columns
+        const int kv_left = p.kv_len - key0;
+        uint32_t r[64];
+        const uint32_t s_addr = lane_base + (t * 2 + b) * 128 + h * 64;
+        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(bar(MQ_S_EMPTY + t * 2 + b));          // the scores are in registers: free the buffer
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          float mx = __uint_as_float(r[w * 32]);
+#pragma unroll
+          for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[w * 32 + i]));
+          if (__any_sync(0xffffffffu, mx > thr)) {
+            uint32_t m = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (__uint_as_float(r[w * 32 + i]) > thr) m |= 1u << i;
+            const int lim = kv_left - w * 32;              // live columns of this quarter
+            m &= (lim >= 32) ? 0xffffffffu : (lim <= 0 ? 0u : ((1u << lim) - 1u));
+            const uint32_t bits = __reduce_or_sync(0xffffffffu, m);
+            // the caller-zeroed mask is only ever set to 1 (by up to four warps of 32 rows each)
+            if (block_in && ((bits >> lane) & 1u)) mrow0[key0 + w * 32 + lane] = 1;
+          }
+        }
+      }
+    } else if (active) {
       bool ok = true;
       OnlineState st;
       online_init(st);

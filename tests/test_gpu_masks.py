@@ -126,6 +126,16 @@ def test_token_mask_inside_kept_blocks(S, D, kv):
         assert not (got[..., n_kv:] != 0).any()
     diff = (listed[..., :n_kv].cpu() > 0) ^ (plain[..., :n_kv].cpu() > 0)
     assert not (diff & ~near).any()
+    # the mask over all key tiles has two kernels (two threads per row by default, "maxq_wide" = 0: the dense
+    # family's mode); same comparison against the same threshold, so the same mask bit for bit
+    narrow = torch.full_like(listed, 9)
+    capi.set_tuning("maxq_wide", 0)
+    try:
+        capi.booleanmask_128(narrow, m, l, q, k, w.tau, kv_seq_len=kv)
+        capi.check()
+    finally:
+        capi.set_tuning("maxq_wide", -1)
+    assert torch.equal(narrow, plain)
     # thread blocks in storage order instead of longest lists first: the same mask
     unordered = torch.full_like(listed, 9)
     capi.booleanmask_128_listed(unordered, m, l, q, k, w.tau, idx, cnt, kv_seq_len=kv, ordered=False)
