@@ -50,8 +50,8 @@ int fgattn_last_cuda_error(void);
  * less-than-half-full last wave of thread blocks into their two query tiles (1 = default, negative = back
  * to FGATTN_DENSE_HALVES); "token_block_route": 1 allows the
  * block route of fgattn_sp_attn (given the large workspace), 0 keeps it on the row gather (default),
- * negative = back to FGATTN_TOKEN_BLOCK_ROUTE; "maxq_wide": 0 runs the max / denominator pass on the dense
- * family's own mode instead of the two-threads-per-row kernel (1 / -1 = default, below -1 = back to
+ * negative = back to FGATTN_TOKEN_BLOCK_ROUTE; "maxq_wide": 0 runs the max / denominator pass and the token mask
+ * over all key tiles on the dense family's own modes instead of the two-threads-per-row kernel (1 / -1 = default, below -1 = back to
  * FGATTN_MAXQ_WIDE). */
 int fgattn_set_tuning(const char* name, int value);
 /* Synchronise `stream` and report whether any kernel launched through this library on the current
