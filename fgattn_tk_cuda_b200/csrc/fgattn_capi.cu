@@ -162,6 +162,10 @@ int launch_dense_k(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
 }
 
 constexpr int kPersistMaxKeyTiles = 8;     // persistent CTAs up to 1024 keys
+// The max / denominator pass alone stays persistent up to 2048 keys: measured against its one-item kernel
+// (maxq_pass.cuh) at 32768 queries x 40 heads, D = 128 / 64: 1280 keys 16 / 12 % faster, 1536 keys 13 / 6 %,
+// 2048 keys 10 / 4 %, 3072 keys level / 1 % slower
+constexpr int kPersistMaxKeyTilesMaxq = 16;
 
 // The max / denominator pass with two threads per row (maxq_pass.cuh); same parameters and grid as the
 // one-item form of the dense family.
@@ -183,7 +187,8 @@ int launch_dense_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
   pp.n_items = pp.n_pairs * nbh;
   if constexpr (MODE != fg::kTokenMask && !BLOCKMAX) {
     const int persist_env = env_dense_persist();
-    const bool persist = persist_env >= 0 ? persist_env != 0 : p.n_kv_tiles <= kPersistMaxKeyTiles;
+    const bool persist = persist_env >= 0 ? persist_env != 0
+                                          : p.n_kv_tiles <= (MODE == fg::kML ? kPersistMaxKeyTilesMaxq : kPersistMaxKeyTiles);
     if (persist) {
       int sms = 0;
       int r = sm_count(&sms);

@@ -132,6 +132,7 @@ def test_maxq_two_threads_per_row(B, H, S, D, kv):
     nqb = nkb = (S + 63) // 64
     out = {}
     try:
+        capi.set_tuning("dense_persist", 0)      # up to 2048 keys maxq_denom alone would take the persistent form
         for wide in (1, 0):
             capi.set_tuning("maxq_wide", wide)
             m, l = _ml_buffers(B, H, S)
@@ -148,6 +149,7 @@ def test_maxq_two_threads_per_row(B, H, S, D, kv):
             out[wide] = (m.cpu(), l.cpu(), idx.cpu(), cnt.cpu())
     finally:
         capi.set_tuning("maxq_wide", -1)
+        capi.set_tuning("dense_persist", -1)
     assert torch.equal(out[0][0], out[1][0])
     np.testing.assert_allclose(out[0][1][..., :S].numpy(), out[1][1][..., :S].numpy(), rtol=5e-4)   # approximate exponentials, different summation order
     # a block whose probability lies within 1e-3 of the threshold may flip with the summation order of l
