@@ -379,7 +379,12 @@ def main():
         ms_full = ev_time(lambda: capi.full_attn(o, q, k, v), 5, 2)
         ms_lists = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch), 5, 2)
         ms_maxq = ev_time(lambda: capi.maxq_denom(max_q, denom, q, k), 5, 2)
-        mask_bytes = B * H * (4.0 * s_pad * nkb * 2 + 8.0 * S + 4.0 * nqb * nkb + 4.0 * nqb)
+        # the threshold + compaction step alone, on the block maxima the list build above left in the scratch
+        idx_t, cnt_t = torch.empty_like(idx), torch.empty_like(cnt)
+        ms_thresh = ev_time(lambda: capi.block_lists_from_maxima(idx_t, cnt_t, scratch, max_q, denom, q.shape, w.tau), 10, 3)
+        thresh_same = bool(torch.equal(idx_t, idx) and torch.equal(cnt_t, cnt))
+        del idx_t, cnt_t
+        thresh_bytes = B * H * (4.0 * s_pad * nkb + 8.0 * S + 4.0 * nqb * nkb + 4.0 * nqb)
         ms_build = ev_time(lambda: capi.block_index_lists(idx, cnt, max_q, denom, q, k, w.tau, scratch, o=o, v=v), 5, 2)
         # threshold token mask (reference granularity): the full second Q K^T pass against the pass that only
         # visits the kept 64x64 blocks
@@ -426,10 +431,12 @@ def main():
             "full_attn_frac_of_peak": F_full / ms_full / 1e9 / peak,
             "block_lists_ms": ms_lists, "block_lists_qk_tflops": F_full / 2 / ms_lists / 1e9,
             "maxq_denom_ms": ms_maxq, "maxq_denom_qk_tflops": F_full / 2 / ms_maxq / 1e9,
-            "mask_epilogue_note": "block_lists_ms - maxq_denom_ms (difference of two timings)",
-            "mask_epilogue_ms": ms_lists - ms_maxq,
-            "mask_epilogue_gbs": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6,
-            "mask_epilogue_frac_of_hbm_peak": mask_bytes / max(ms_lists - ms_maxq, 1e-6) / 1e6 / peaks["hbm_gbs"],
+            # the threshold + compaction kernel timed by itself (block_lists_from_maxima on the maxima of the list
+            # build): reads the maxima once, writes lists and counts
+            "threshold_lists_ms": ms_thresh, "threshold_lists_gbs": thresh_bytes / ms_thresh / 1e6,
+            "threshold_lists_frac_of_hbm_peak": thresh_bytes / ms_thresh / 1e6 / peaks["hbm_gbs"],
+            "threshold_lists_match_list_build": thresh_same,
+            "block_maxima_scratch_bytes": 4.0 * B * H * s_pad * nkb,
             "booleanmask_128_ms": ms_tokmask, "booleanmask_128_listed_ms": ms_tokmask_listed,
             "pack_mask_ms": ms_pack, "pack_mask_gbs": pack_bytes / ms_pack / 1e6,
             "pack_mask_frac_of_hbm_peak": pack_bytes / ms_pack / 1e6 / peaks["hbm_gbs"],

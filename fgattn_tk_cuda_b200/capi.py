@@ -39,6 +39,7 @@ PROTOTYPES = {
     "fgattn_block_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "fgattn_block_index_lists": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _f, _vp,
                                       _sz, _vp]),
+    "fgattn_block_lists_from_maxima": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f, _vp]),
     "fgattn_block_index_lists_noalloc": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _f,
                                               _vp]),
     "fgattn_sp_attn_blocks_ml": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _sz,
@@ -218,6 +219,17 @@ def block_index_lists(kb_indices, kb_counts, max_q, denom, q, k, threshold, scra
         _call("fgattn_block_index_lists", _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3], _ptr(max_q),
               _ptr(denom), _ptr(o), _ptr(q), _ptr(k), _ptr(v), float(threshold), B, H, S, D, k.shape[2],
               kv_seq_len or k.shape[2], scale, _ptr(scratch), scratch.numel() * scratch.element_size(), _stream(q))
+
+
+def block_lists_from_maxima(kb_indices, kb_counts, block_maxima, max_q, denom, q_shape, threshold, kv_seq_len=None,
+                            scale=0.0):
+    """The threshold step alone on the block maxima that block_index_lists left in a scratch sized for all units
+    (q_shape = (B, H, S, D) of that call): lists for another threshold without a new pass over the keys."""
+    B, H, S, D = q_shape
+    with torch.cuda.device(kb_indices.device):
+        _call("fgattn_block_lists_from_maxima", _ptr(kb_indices), _ptr(kb_counts), kb_indices.shape[3],
+              _ptr(block_maxima), _ptr(max_q), _ptr(denom), float(threshold), B, H, S, D, kv_seq_len or S, scale,
+              _stream(kb_indices))
 
 
 NOALLOC_SCRATCH_BYTES = 64 << 20

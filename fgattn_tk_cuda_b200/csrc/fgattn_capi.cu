@@ -692,6 +692,23 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
   return FGATTN_OK;
 }
 
+int fgattn_block_lists_from_maxima(int* kb_indices, int* kb_counts, int list_stride, const float* block_maxima,
+                                   const float* max_q, const float* denom, float threshold, int batch, int heads,
+                                   int seq, int D, int kv_seq_len, float scale, void* stream) {
+  if (!kb_indices || !kb_counts || !block_maxima || !max_q || !denom || !(threshold > 0.f)) return FGATTN_INVALID_ARGUMENT;
+  if (batch <= 0 || heads <= 0 || seq <= 0 || kv_seq_len <= 0) return FGATTN_INVALID_ARGUMENT;
+  if (D != 64 && D != 128) return FGATTN_UNSUPPORTED;
+  if ((long long)batch * heads > 65535) return FGATTN_UNSUPPORTED;
+  const int nkb = (kv_seq_len + 63) / 64, nqb = (seq + 63) / 64, s_pad = ((seq + 127) / 128) * 128;
+  if (list_stride < nkb) return FGATTN_INVALID_ARGUMENT;
+  const int smem = 64 * int(sizeof(float)) + ((nkb + 15) / 16) * 16;
+  fg::block_threshold_compact_kernel<<<dim3(nqb, batch * heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      block_maxima, max_q, denom, kb_indices, kb_counts, seq, s_pad, nqb, nkb, list_stride, 0, resolve_scale_log2(scale, D),
+      log2f(threshold));
+  FG_CUDA(cudaGetLastError());
+  return FGATTN_OK;
+}
+
 // ---- allocation-free variant of fgattn_block_index_lists --------------------------------------
 namespace {
 // First use on a device: resolve the device addresses of the built-in arrays (no allocation).

@@ -152,6 +152,17 @@ int fgattn_block_index_lists(int* kb_indices, int* kb_counts, int list_stride, f
                              int seq, int D, int kv_rows, int kv_seq_len, float scale, void* scratch,
                              size_t scratch_bytes, void* stream);
 
+/* The threshold step of fgattn_block_index_lists alone, on block maxima that an earlier call left behind:
+ * when that call was given scratch for all batch*heads units (fgattn_block_scratch_bytes), the scratch holds,
+ * as fp32 [B*H][nkb][ceil(seq/128)*128], the raw maximum of Q K^T per query row and 64-key block, and together
+ * with the max_q / denom of the same call this entry point builds the lists for ANOTHER threshold without a
+ * new pass over the keys (what the reference can only do by re-running booleanmask_128,
+ * python/spattn/mask_utils.py:306-334).  HBM-bound: reads the maxima once, writes lists and counts.
+ * Same list layout and rules as fgattn_block_index_lists; scale and D only set the softmax scale. */
+int fgattn_block_lists_from_maxima(int* kb_indices, int* kb_counts, int list_stride, const float* block_maxima,
+                                   const float* max_q, const float* denom, float threshold, int batch, int heads,
+                                   int seq, int D, int kv_seq_len, float scale, void* stream);
+
 /* Largest scratch the library itself can lend: see fgattn_block_index_lists_noalloc. */
 #define FGATTN_NOALLOC_SCRATCH_BYTES (64u << 20)
 

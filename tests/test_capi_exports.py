@@ -55,6 +55,8 @@ def test_argument_validation_needs_no_device():
                                              null, 0, null) == 1
     assert lib.fgattn_booleanmask_128_listed(buf, 1e-3, 128, buf, buf, buf, buf, buf, buf, 4, 1, 1, 64, 64, 64, 64, 0.0,
                                              buf, 8, null) == 7
+    assert lib.fgattn_block_lists_from_maxima(buf, buf, 4, null, buf, buf, 1e-3, 1, 1, 64, 64, 64, 0.0, null) == 1
+    assert lib.fgattn_block_lists_from_maxima(buf, buf, 0, buf, buf, buf, 1e-3, 1, 1, 64, 64, 64, 0.0, null) == 1   # list too narrow
     assert lib.fgattn_sp_attn(buf, buf, buf, buf, buf, null, 128, 1, 1, 64, 64, 64, 0.0, null, 0, null) == 1
     assert lib.fgattn_sp_attn(buf, buf, buf, buf, buf, buf, 128, 1, 1, 64, 64, 64, 0.0, buf, 8, null) == 7
     assert lib.fgattn_sp_attn_blocks(buf, buf, buf, buf, null, buf, 4, 1, 1, 64, 64, 64, 64, 0.0, null, 0, null) == 1

@@ -225,3 +225,35 @@ def _order_case(capi, orc):
     capi.check()
     assert torch.equal(t_st, t_or)
     assert torch.isfinite(t_or.float()).all()
+
+
+@pytest.mark.parametrize("S,D,kv", [(1000, 128, None), (1536, 64, 1400)])
+def test_lists_for_another_threshold_from_kept_maxima(S, D, kv):
+    """block_lists_from_maxima: the threshold step alone on the block maxima that block_index_lists left in a
+    scratch sized for all units.  The same threshold gives the same lists; another threshold gives the lists of a
+    fresh pass with that threshold."""
+    from fgattn_tk_cuda_b200 import capi, synth
+    w = synth.Workload("t", 2, 3, S, D, "clustered", centroids=10, run=80, tau=1e-3, seed=77)
+    q, k, _ = synth.make_qkv(w, device="cuda")
+    B, H = q.shape[:2]
+    n_kv = kv or S
+    nqb, nkb = (S + 63) // 64, (n_kv + 63) // 64
+    s_pad = 128 * ((S + 127) // 128)
+    def fresh(tau):
+        idx = torch.full((B, H, nqb, nkb), -7, dtype=torch.int32, device="cuda")
+        cnt = torch.full((B, H, nqb), -7, dtype=torch.int32, device="cuda")
+        m = torch.empty(B, H, 1, s_pad, device="cuda")
+        l = torch.empty_like(m)
+        scratch = torch.empty(capi.block_scratch_bytes(B, H, S, n_kv) // 4, device="cuda")
+        capi.block_index_lists(idx, cnt, m, l, q, k, tau, scratch, kv_seq_len=kv)
+        capi.check()
+        return idx, cnt, m, l, scratch
+    idx, cnt, m, l, scratch = fresh(w.tau)
+    for tau in (w.tau, 3e-2):
+        idx2 = torch.full_like(idx, -9)
+        cnt2 = torch.full_like(cnt, -9)
+        capi.block_lists_from_maxima(idx2, cnt2, scratch, m, l, q.shape, tau, kv_seq_len=kv)
+        capi.check()
+        ref_idx, ref_cnt = (idx, cnt) if tau == w.tau else fresh(tau)[:2]
+        assert torch.equal(cnt2, ref_cnt) and torch.equal(idx2, ref_idx)
+    assert cnt2.sum().item() < cnt.sum().item()          # the higher threshold keeps fewer blocks
