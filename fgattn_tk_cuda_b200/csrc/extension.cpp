@@ -276,6 +276,40 @@ void block_index_lists(torch::Tensor kb_indices, torch::Tensor kb_counts, torch:
                "block_index_lists");
 }
 
+// The threshold step alone on the block maxima that block_index_lists left in a scratch sized for all units:
+// key-block lists for another threshold without a new pass over the keys.  The lists give B, H and ceil(S/64).
+void block_lists_from_maxima_check(torch::Tensor kb_indices, torch::Tensor kb_counts, torch::Tensor block_maxima,
+                                   torch::Tensor max_q, torch::Tensor denom, int64_t seq, int64_t head_dim,
+                                   int64_t kv_seq_len, double threshold) {
+  check_dtype(kb_indices, at::kInt, "kb_indices"); check_dtype(kb_counts, at::kInt, "kb_counts");
+  check_dtype(block_maxima, at::kFloat, "block_maxima");
+  check_dtype(max_q, at::kFloat, "max_q"); check_dtype(denom, at::kFloat, "denom");
+  TORCH_CHECK(seq > 0 && kv_seq_len > 0, "seq and kv_seq_len must be positive");
+  TORCH_CHECK(head_dim == 64 || head_dim == 128, "head_dim must be 64 or 128");
+  TORCH_CHECK(threshold > 0.0, "threshold must be positive");
+  const int64_t nqb = cdiv(seq, 64), nkb = cdiv(kv_seq_len, 64);
+  TORCH_CHECK(kb_indices.dim() == 4 && kb_indices.size(2) == nqb && kb_indices.size(3) >= nkb,
+              "kb_indices must be [B, H, ceil(S/64), >= ceil(S_kv/64)]");
+  const int64_t bh = kb_indices.size(0) * kb_indices.size(1);
+  TORCH_CHECK(kb_counts.numel() == bh * nqb, "kb_counts must hold B*H*ceil(S/64) counts");
+  TORCH_CHECK(max_q.numel() >= bh * pad128(seq) && denom.numel() >= bh * pad128(seq),
+              "max_q and denom must hold B*H*ceil(S/128)*128 floats");
+  TORCH_CHECK(block_maxima.numel() >= bh * nkb * pad128(seq),
+              "block_maxima must hold B*H*ceil(S_kv/64)*ceil(S/128)*128 floats (the scratch of a list build for all units)");
+}
+void block_lists_from_maxima(torch::Tensor kb_indices, torch::Tensor kb_counts, torch::Tensor block_maxima,
+                             torch::Tensor max_q, torch::Tensor denom, int64_t seq, int64_t head_dim,
+                             int64_t kv_seq_len, double threshold) {
+  block_lists_from_maxima_check(kb_indices, kb_counts, block_maxima, max_q, denom, seq, head_dim, kv_seq_len, threshold);
+  c10::cuda::CUDAGuard guard(kb_indices.device());
+  check_status(fgattn_block_lists_from_maxima(kb_indices.data_ptr<int>(), kb_counts.data_ptr<int>(),
+                                              int(kb_indices.size(3)), block_maxima.data_ptr<float>(),
+                                              max_q.data_ptr<float>(), denom.data_ptr<float>(), float(threshold),
+                                              kb_indices.size(0), kb_indices.size(1), int(seq), int(head_dim),
+                                              int(kv_seq_len), 0.f, stream_of(kb_indices)),
+               "block_lists_from_maxima");
+}
+
 void sp_attn_blocks_ml_check(torch::Tensor o, torch::Tensor q, torch::Tensor k, torch::Tensor v,
                              torch::Tensor kb_indices, torch::Tensor kb_counts, torch::Tensor max_q,
                              torch::Tensor denom) {
@@ -440,6 +474,7 @@ TORCH_LIBRARY_FRAGMENT(cuda_attn, m) {
   // block-granular additions
   m.def("booleanmask_128_listed(Tensor (booleanmask!) booleanmask, Tensor o_max_q, Tensor o_denom, Tensor q, Tensor k, float threshold, Tensor kb_indices, Tensor kb_counts) -> ()");
   m.def("block_index_lists(Tensor (kb_indices!) kb_indices, Tensor (kb_counts!) kb_counts, Tensor (o_max_q!) o_max_q, Tensor (o_denom!) o_denom, Tensor(o!)? o, Tensor q, Tensor k, Tensor? v, float threshold, Tensor (scratch!) scratch) -> ()");
+  m.def("block_lists_from_maxima(Tensor (kb_indices!) kb_indices, Tensor (kb_counts!) kb_counts, Tensor block_maxima, Tensor max_q, Tensor denom, int seq, int head_dim, int kv_seq_len, float threshold) -> ()");
   m.def("sp_attn_blocks_ml(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts, Tensor max_q, Tensor denom) -> ()");
   m.def("sp_attn_blocks(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts) -> ()");
   m.def("sp_attn_blocks_hint(Tensor (o!) o, Tensor q, Tensor k, Tensor v, Tensor kb_indices, Tensor kb_counts, Tensor max_q_hint) -> ()");
@@ -464,6 +499,7 @@ TORCH_LIBRARY_IMPL(cuda_attn, Meta, m) {
   m.impl("booleanmask_to_indexmask", booleanmask_to_indexmask_check);
   m.impl("booleanmask_128_listed", booleanmask_128_listed_check);
   m.impl("block_index_lists", block_index_lists_check);
+  m.impl("block_lists_from_maxima", block_lists_from_maxima_check);
   m.impl("sp_attn_blocks_ml", sp_attn_blocks_ml_check);
   m.impl("sp_attn_blocks", sp_attn_blocks_check);
   m.impl("sp_attn_blocks_hint", sp_attn_blocks_hint_check);
@@ -484,6 +520,7 @@ TORCH_LIBRARY_IMPL(cuda_attn, CUDA, m) {
   m.impl("booleanmask_to_indexmask", booleanmask_to_indexmask);
   m.impl("booleanmask_128_listed", booleanmask_128_listed);
   m.impl("block_index_lists", block_index_lists);
+  m.impl("block_lists_from_maxima", block_lists_from_maxima);
   m.impl("sp_attn_blocks_ml", sp_attn_blocks_ml);
   m.impl("sp_attn_blocks", sp_attn_blocks);
   m.impl("sp_attn_blocks_hint", sp_attn_blocks_hint);
@@ -504,6 +541,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fullattn_maxq_denom", &fullattn_maxq_denom, "fullattn_maxq_denom");
   m.def("booleanmask_128_listed", &booleanmask_128_listed, "token mask inside the kept 64x64 blocks");
   m.def("block_index_lists", &block_index_lists, "one-pass m/l + key-block lists");
+  m.def("block_lists_from_maxima", &block_lists_from_maxima, "key-block lists for another threshold from kept block maxima");
   m.def("sp_attn_blocks_ml", &sp_attn_blocks_ml, "block-sparse attention, precomputed m/l");
   m.def("sp_attn_blocks", &sp_attn_blocks, "block-sparse attention, renormalising");
   m.def("sp_attn_blocks_hint", &sp_attn_blocks_hint, "block-sparse attention, renormalising, row-maximum hint");

@@ -256,4 +256,9 @@ def test_lists_for_another_threshold_from_kept_maxima(S, D, kv):
         capi.check()
         ref_idx, ref_cnt = (idx, cnt) if tau == w.tau else fresh(tau)[:2]
         assert torch.equal(cnt2, ref_cnt) and torch.equal(idx2, ref_idx)
+        # the same through the torch operator
+        import fgattn_tk_cuda_b200.spattn  # noqa: F401  (registers torch.ops.cuda_attn)
+        idx3, cnt3 = torch.full_like(idx, -9), torch.full_like(cnt, -9)
+        torch.ops.cuda_attn.block_lists_from_maxima(idx3, cnt3, scratch, m, l, S, D, n_kv, tau)
+        assert torch.equal(cnt3, ref_cnt) and torch.equal(idx3, ref_idx)
     assert cnt2.sum().item() < cnt.sum().item()          # the higher threshold keeps fewer blocks
