@@ -13,6 +13,7 @@ SHAPES = [  # B, H, S_q, S_kv, D, kv_seq_len
     (2, 2, 512, 200, 64, None),
     (1, 2, 257, 1000, 128, 777),
     (1, 2, 640, 130, 64, 100),
+    (1, 2, 300, 2500, 64, 2345),       # more than 2048 keys: the one-item kernels of the max / denominator pass
 ]
 
 
