@@ -118,7 +118,7 @@ enum : int {
   PB_S_EMPTY = 34,     // +score buffer (3): the P*V product that read the buffer's probabilities is done
   PB_O_FULL = 37,
   PB_O_EMPTY = 38,
-  PB_P_FULL = 40,      // +(step % 6) * 2 + key block of the step (12)
+  PB_P_FULL = 40,      // +(step % 6) * 2: both key blocks of the step (eight warps arrive)
   PB_L_FULL = 52,      // +(item % 4) (4): RENORM, the item's partial row sums are in shared memory
   PB_COUNT = 56
 };
@@ -222,7 +222,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     for (int b = 0; b < kSB; ++b) mbar_init(bar(PB_S_EMPTY + b), 1);
     for (int i = 0; i < 6; ++i) {
       mbar_init(bar(PB_S_FULL + i), 1);
-      for (int kb = 0; kb < 2; ++kb) mbar_init(bar(PB_P_FULL + i * 2 + kb), 4);
+      mbar_init(bar(PB_P_FULL + i * 2), 8);        // both warpgroups of the pair: four warps each
     }
     for (int s = 0; s < 4; ++s) {
       mbar_init(bar(PB_K_FULL + s), 1);
@@ -476,28 +476,23 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           const int vs = s % Cfg::kVStages, pbuf = s % kSB;
           FG_TW(w_v, ok = mbar_wait_warp(bar(PB_V_FULL + vs), (s / Cfg::kVStages) & 1, ab, p.err, 1303));
           const uint32_t va = sbase + Cfg::kOffV + vs * Cfg::kTileBytes;
-          // the step's two key blocks come from the two warpgroups of the pair that owns the step
-          for (int kb = 0; kb < 2 && ok; ++kb) {
-            FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + (s % 6) * 2 + kb), (s / 6) & 1, ab, p.err, 1304));
-            if (!ok) break;
-            tc_fence_after();
-            if (!(dbg & 2)) {
-              if (elect_one()) {
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                  const int ks = kb * 4 + kk;                   // 16-key step inside the 128-key tile
-                  umma_ts(tmem + kColO, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8,
-                          umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                  if constexpr (TSUM)                          // l += P * 1
-                    umma_ts(tmem + kColL, tmem + kColS + pbuf * 128 + kb * 64 + kk * 8, ones_desc, idesc_l,
-                            (j > 0 || ks > 0) ? 1u : 0u);
-                }
-              }
-              __syncwarp();
-            }
-          }
+          // the step's two key blocks come from the two warpgroups of the pair that owns the step; one wait for
+          // both and one elected lane for the whole product and its commits (a wait per key block, so that the
+          // first four instructions could go ahead of the second block's probabilities, was 1-3 % slower)
+          FG_TW(w_p, ok = mbar_wait_warp(bar(PB_P_FULL + (s % 6) * 2), (s / 6) & 1, ab, p.err, 1304));
           if (!ok) break;
+          tc_fence_after();
           if (elect_one()) {
+            if (!(dbg & 2)) {
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks) {                  // 16-key step inside the 128-key tile
+                umma_ts(tmem + kColO, tmem + kColS + pbuf * 128 + (ks / 4) * 64 + (ks % 4) * 8,
+                        umma_smem_desc_sw128(va + ks * 2048, 16384, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                if constexpr (TSUM)                          // l += P * 1
+                  umma_ts(tmem + kColL, tmem + kColS + pbuf * 128 + (ks / 4) * 64 + (ks % 4) * 8, ones_desc, idesc_l,
+                          (j > 0 || ks > 0) ? 1u : 0u);
+              }
+            }
             umma_commit(bar(PB_V_EMPTY + vs));
             umma_commit(bar(PB_S_EMPTY + pbuf));           // scores and probabilities of this buffer are consumed
             if (j == n - 1) umma_commit(bar(PB_O_FULL));
@@ -666,7 +661,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(PB_P_FULL + (s % 6) * 2 + kb_sel));
+          if (lane == 0) mbar_arrive(bar(PB_P_FULL + (s % 6) * 2));
           t_st += FG_CLK() - ts0;
           if (pe) {                                      // pending rows of the previous item
             epilogue();
