@@ -23,7 +23,8 @@
 // Barriers that a role waits on only every other step (score-full, probability-full) exist once per
 // (buffer, pair), i.e. per step mod 6, because a parity wait must see every phase of its barrier.
 // Service warps after the softmax warps: TMA producer of Q and the K ring, Q K^T issuer, scheduler
-// (queue + union lists, up to three items ahead), P V issuer, TMA producer of the V ring.
+// (queue + union lists; it builds the next item's union bitmaps while it waits for a free list buffer), P V issuer,
+// TMA producer of the V ring.
 //
 // RENORM = true is the renormalising form (softmax over the kept keys only, what the sp_attn operator
 // computes) on the same schedule.  A softmax is invariant under a shift of its exponents, and the
@@ -255,8 +256,9 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     for (;; ++it) {
       const int lb = it % NLB;
       bool ok = true;
-      if (it >= NLB) FG_TW(w_le, ok = mbar_wait_relaxed(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001));
-      if (!ok) break;
+      // Everything that needs global memory -- the queue, the item's two lists -- and the union bitmaps (private
+      // to this warp) come BEFORE the wait for a free list buffer, so that only the scan is left when the readers
+      // of the item before last let go of it.
       int g = 0, item = 0;
       for (;;) {                                           // next item of the queue that is routed to this kernel
         if (lane == 0) g = atomicAdd(p.queue, 1);
@@ -265,63 +267,57 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
         item = p.order[g];
         if (!TOKEN || !p.route || p.route[item] != 0) break;
       }
-      if (g >= p.n_items) {
+      const bool done = g >= p.n_items;
+      int bh = 0, pair = 0;
+      int n_half[2] = {0, 0};
+      if (!done) {
+        bh = item / p.npairs;
+        pair = item - bh * p.npairs;
+        constexpr bool token_lists = TOKEN;
+        const int list_rows = token_lists ? p.npairs : p.nqb;
+        for (int w = lane; w < 2 * words; w += 32) bm0[w] = 0u;
+        __syncwarp();
+        // both halves' counts are fetched before either list is walked
+        const int* src_half[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int qb = token_lists ? pair : pair * 2 + half;     // token lists: both halves walk the one list
+          src_half[half] = p.kb_idx;
+          if (qb < list_rows) {
+            src_half[half] = p.kb_idx + (size_t(bh) * list_rows + qb) * p.list_stride;
+            n_half[half] = min(p.kb_cnt[size_t(bh) * list_rows + qb], p.list_stride);
+          }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t* bm = half ? bm1 : bm0;
+          for (int i = lane; i < n_half[half]; i += 32) {
+            const int kb = src_half[half][i];
+            if (kb >= 0 && kb < p.nkb) atomicOr(&bm[kb >> 5], 1u << (kb & 31));
+          }
+        }
+        __syncwarp();
+      }
+      if (it >= NLB) FG_TW(w_le, ok = mbar_wait_relaxed(bar(PB_LIST_EMPTY + lb), ((it / NLB) - 1) & 1, ab, p.err, 1001));
+      if (!ok) break;
+      if (done) {
         if (lane == 0) {
           info[lb].n_steps = -1;
           mbar_arrive(bar(PB_LIST_FULL + lb));
         }
         break;
       }
-      const int bh = item / p.npairs;
-      const int pair = item - bh * p.npairs;
-      constexpr bool token_lists = TOKEN;
-      const int list_rows = token_lists ? p.npairs : p.nqb;
-      for (int w = lane; w < 2 * words; w += 32) bm0[w] = 0u;
-      __syncwarp();
-      // both halves' counts are fetched before either list is walked
-      int n_half[2];
-      const int* src_half[2];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int qb = token_lists ? pair : pair * 2 + half;     // token lists: both halves walk the one list
-        n_half[half] = 0;
-        src_half[half] = p.kb_idx;
-        if (qb < list_rows) {
-          src_half[half] = p.kb_idx + (size_t(bh) * list_rows + qb) * p.list_stride;
-          n_half[half] = min(p.kb_cnt[size_t(bh) * list_rows + qb], p.list_stride);
-        }
-      }
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t* bm = half ? bm1 : bm0;
-        for (int i = lane; i < n_half[half]; i += 32) {
-          const int kb = src_half[half][i];
-          if (kb >= 0 && kb < p.nkb) atomicOr(&bm[kb >> 5], 1u << (kb & 31));
-        }
-      }
-      __syncwarp();
+      // ascending union list: lane j looks at key block 32 w + j of bitmap word w, the word itself is the ballot
       uint32_t* out = lists + lb * p.list_cap;
       int base = 0;
-      for (int w0 = 0; w0 < words; w0 += 32) {
-        const int w = w0 + lane;
-        const uint32_t a = (w < words) ? bm0[w] : 0u, bb = (w < words) ? bm1[w] : 0u;
-        uint32_t u = a | bb;
-        const int cnt = __popc(u);
-        int incl = cnt;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int n = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += n;
+      for (int w = 0; w < words; ++w) {
+        const uint32_t a = bm0[w], bb = bm1[w];
+        const uint32_t u = a | bb;
+        if ((u >> lane) & 1u) {
+          const int off = base + __popc(u & ((1u << lane) - 1u));
+          if (off < p.list_cap) out[off] = uint32_t(w * 32 + lane) | (((a >> lane) & 1u) << 30) | (((bb >> lane) & 1u) << 31);
         }
-        int off = base + incl - cnt;
-        while (u) {
-          const int bit = __ffs(u) - 1;
-          u &= u - 1;
-          if (off < p.list_cap)
-            out[off] = uint32_t(w * 32 + bit) | (((a >> bit) & 1u) << 30) | (((bb >> bit) & 1u) << 31);
-          ++off;
-        }
-        base += __shfl_sync(0xffffffffu, incl, 31);
+        base += __popc(u);
       }
       if (base > p.list_cap - 1) base = p.list_cap - 1;
       __syncwarp();
