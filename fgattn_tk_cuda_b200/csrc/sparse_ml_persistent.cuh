@@ -405,7 +405,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     const uint32_t idesc_qk = umma_idesc_bf16(128, 128, false);
     int s = 0, u = 0;
     bool ok = true;
-    long long w_k = 0, w_se = 0, w_misc = 0, t_start = FG_CLK();
+    long long w_k = 0, w_se = 0, w_misc = 0, w_q = 0, t_start = FG_CLK();
     for (int it = 0; ok; ++it) {
       const int lb = it % NLB;
       FG_TW(w_misc, ok = mbar_wait_warp(bar(PB_LIST_FULL + lb), (it / NLB) & 1, ab, p.err, 1201));
@@ -416,7 +416,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
       __syncwarp();
       if (n > 0) {
         const int qb = u & 1;
-        FG_TW(w_misc, ok = mbar_wait_warp(bar(PB_Q_FULL + qb), (u >> 1) & 1, ab, p.err, 1202));
+        FG_TW(w_q, ok = mbar_wait_warp(bar(PB_Q_FULL + qb), (u >> 1) & 1, ab, p.err, 1202));
         const uint32_t qa = sbase + Cfg::kOffQ + qb * Cfg::kTileBytes;
         for (int j = 0; j < n && ok; ++j, ++s) {
           const int ks = s % Cfg::kKStages, sbuf = s % kSB;
@@ -446,7 +446,7 @@ sparse_ml_persistent_kernel(const __grid_constant__ CUtensorMap mq, const __grid
     }
     if (p.stats && lane == 0) {
       long long* st_ = p.stats + size_t(blockIdx.x) * 32;
-      st_[0] = FG_CLK() - t_start; st_[1] = w_k; st_[2] = w_se; st_[3] = w_misc; st_[4] = s;
+      st_[0] = FG_CLK() - t_start; st_[1] = w_k; st_[2] = w_se; st_[3] = w_misc; st_[4] = s; st_[13] = w_q;
     }
   } else if (warp == Cfg::kWarpPV) {
     // ------------------------------------------------------------------ P V issuer
